@@ -48,6 +48,7 @@ class KvNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # keys a query sees, itself included; None = all
+    planes: int = 2               # 2: keys and values; 1: one tensor per position that serves as both (a latent)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -143,7 +144,7 @@ class CacheManager:
 
     def bytes_per_page(self, group: int, element_size: int) -> int:
         g = self.groups[group]
-        return g.layers * 2 * self.page_size * g.need.num_kv_heads * g.need.head_dim * element_size
+        return g.layers * g.need.planes * self.page_size * g.need.num_kv_heads * g.need.head_dim * element_size
 
     def bytes_per_token(self, element_size: int) -> int:
         """Cache bytes one position costs over all groups (windows not counted as savings)."""
@@ -169,7 +170,7 @@ class CacheManager:
 
             for g in self.groups:
                 g.tensor = torch.zeros(
-                    (g.layers, 2, num_pages, self.page_size, g.need.num_kv_heads, g.need.head_dim),
+                    (g.layers, g.need.planes, num_pages, self.page_size, g.need.num_kv_heads, g.need.head_dim),
                     dtype=dtype, device=device)
             for need in self.state_needs:
                 sdtype = dtype if need.dtype == "model" else torch.float32
@@ -181,11 +182,11 @@ class CacheManager:
     # ------------------------------------------------------------------
     def kv_views(self, handle: KvHandle):
         """(k, v, page_stride in elements) of one layer: k and v are views
-        [pages, page_size, kv_heads, head_dim] into the group's tensor."""
+        [pages, page_size, kv_heads, head_dim] into the group's tensor (the same view twice in a group of one plane)."""
         t = self.groups[handle.group].tensor
         if t is None:
             raise RuntimeError("the cache has no device memory (allocate(device=...) first)")
-        return t[handle.layer, 0], t[handle.layer, 1], t.stride(2)
+        return t[handle.layer, 0], t[handle.layer, t.shape[1] - 1], t.stride(2)
 
     def state_tensor(self, state_id: int):
         return self.state_tensors[state_id]

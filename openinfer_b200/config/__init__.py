@@ -10,10 +10,11 @@ from .base import (
     resolve_architecture,
     unregister_architecture,
 )
+from .delunex import DelunexConfig
 from .qwen3 import Qwen3Config
 
 __all__ = [
-    "ArchitectureEntry", "ConfigError", "ModelConfig", "Qwen3Config", "known_architectures",
+    "ArchitectureEntry", "ConfigError", "DelunexConfig", "ModelConfig", "Qwen3Config", "known_architectures",
     "load_config", "read_config_json", "register_architecture", "resolve_architecture",
     "unregister_architecture",
 ]

@@ -131,7 +131,7 @@ def _ensure_builtin() -> None:
 def resolve_architecture(raw: Dict[str, Any]) -> ArchitectureEntry:
     """Pick the one registered architecture that a config.json dict names."""
     _ensure_builtin()
-    archs = raw.get("architectures") or []
+    archs = raw.get("architectures") or raw.get("architecture") or []    # a list, or one name under the singular key
     if isinstance(archs, str):
         archs = [archs]
     hits = [a for a in archs if a in _ARCHITECTURES]

@@ -67,6 +67,24 @@ OI_API int oi_attention_merge_slices(void* out, int out_row_stride, const float*
        const int* row_splits, int nq, int max_splits, int tokens, int hd, void* stream);
 OI_API int oi_attention_tcgen05_status(int* status);
 
+// branch_ops.cu: steps of layers that keep the residual stream in 32-bit (see the file's head)
+OI_API int oi_rmsnorm_cast(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, const int*
+       row_idx, int rows, int hidden, float eps, float w_offset, void* stream);
+OI_API int oi_branch_norm_add(float* h, const void* a, int a_dtype, const void* w, int w_dtype, int rows, int hidden,
+       float eps, float w_offset, float* hist, long long hist_stride, int n_prev, const void* coef, int coef_dtype,
+       void* low, void* stream);
+OI_API int oi_history_average(float* h, float* hist, long long hist_stride, int n_prev, const void* coef, int
+       coef_dtype, long long n, void* stream);
+OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float*
+       state, long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots, int tokens,
+       int requests, int channels, int taps, int add_input, int update_state, void* stream);
+OI_API int oi_latent_store(void* pages, long long page_stride, int page_size, int row_elems, const void* src, long
+       long src_stride, int dtype, const void* w, int w_dtype, const int* slots, int tokens, int rank, float eps,
+       float w_offset, void* stream);
+OI_API int oi_head_gate(void* o, long long o_stride, const void* g, long long g_stride, int dtype, int tokens, int
+       heads, int head_elems, void* stream);
+OI_API int oi_xielu(void* out, const void* in, int dtype, const void* pq, int pq_dtype, long long n, void* stream);
+
 // elementwise.cu
 OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_dtype, const int* ids, int tokens, int
        hidden, int vocab, void* stream);

@@ -51,6 +51,13 @@ _SIGNATURES = {
     "oi_attention_merge_slices": [P, I, P, P, P, I, I, I, I, P],
     "oi_attention_tcgen05_status": [ctypes.POINTER(c_int)],
     "oi_argmax_noalloc": [P, P, I, I, L, P],
+    "oi_rmsnorm_cast": [P, I, P, I, P, I, P, I, I, F, F, P],
+    "oi_branch_norm_add": [P, P, I, P, I, I, I, F, F, P, L, I, P, I, P, P],
+    "oi_history_average": [P, P, L, I, P, I, L, P],
+    "oi_short_conv": [P, I, P, I, P, I, P, L, P, P, P, I, I, I, I, I, I, P],
+    "oi_latent_store": [P, L, I, I, P, L, I, P, I, P, I, I, F, F, P],
+    "oi_head_gate": [P, L, P, L, I, I, I, I, P],
+    "oi_xielu": [P, P, I, P, I, L, P],
 }
 
 

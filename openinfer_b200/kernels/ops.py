@@ -341,3 +341,126 @@ def sample(out: torch.Tensor, logits: torch.Tensor, probs_scratch: torch.Tensor,
                            temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
                            uniform.data_ptr(), _stream()), "sample")
     return out
+
+
+# ---------------------------------------------------------------------------
+# layers with a 32-bit residual stream (csrc/branch_ops.cu)
+# ---------------------------------------------------------------------------
+def rmsnorm_cast(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, *,
+                 row_idx: Optional[torch.Tensor] = None, weight_offset: float = 0.0) -> torch.Tensor:
+    """out = x * rsqrt(mean(x^2) + eps) * (weight_offset + weight) row by row, where x and out may differ in
+    type (a float32 stream normed into the model's type). ``row_idx``: output row r reads x[row_idx[r]]."""
+    _cuda(out, x, weight, row_idx)
+    _i32(row_idx, "rmsnorm_cast row_idx")
+    hidden, rows = x.shape[-1], out.shape[0]
+    if not (out.is_contiguous() and x.is_contiguous() and weight.is_contiguous()) or weight.numel() != hidden \
+            or out.shape[-1] != hidden:
+        raise KernelError(f"rmsnorm_cast: shapes x={tuple(x.shape)} out={tuple(out.shape)} weight={tuple(weight.shape)}")
+    if (row_idx is None and rows != x.shape[0]) or (row_idx is not None and row_idx.numel() != rows):
+        raise KernelError("rmsnorm_cast: row counts do not match")
+    _lib.check(_lib.load().oi_rmsnorm_cast(out.data_ptr(), _code(out, "rmsnorm_cast"), x.data_ptr(), _code(x, "rmsnorm_cast"),
+                                           weight.data_ptr(), _code(weight, "rmsnorm_cast weight"), _ptr(row_idx), rows,
+                                           hidden, float(eps), float(weight_offset), _stream()), "rmsnorm_cast")
+    return out
+
+
+def branch_norm_add(h: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, *, weight_offset: float = 0.0,
+                    history: Optional[torch.Tensor] = None, n_prev: int = 0,
+                    coef: Optional[torch.Tensor] = None, low: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h <- h + a * rsqrt(mean(a^2) + eps) * (weight_offset + weight) (h float32, in place; a float32 or bfloat16).
+    With ``history`` [slots, rows, hidden] float32 and ``coef`` [n_prev + 1]: the sum v is stored as
+    history[n_prev] and h becomes sum_{j < n_prev} coef[j] history[j] + coef[n_prev] v. ``low`` (bfloat16, h's
+    shape) receives the new h rounded, for the product that reads the stream next."""
+    _cuda(h, a, weight, history, coef, low)
+    if low is not None and (low.dtype != torch.bfloat16 or low.shape != h.shape or not low.is_contiguous()):
+        raise KernelError("branch_norm_add: low must be contiguous bfloat16 of h's shape")
+    rows, hidden = h.shape
+    if h.dtype != torch.float32 or a.shape != h.shape or not (h.is_contiguous() and a.is_contiguous() and weight.is_contiguous()) \
+            or weight.numel() != hidden:
+        raise KernelError(f"branch_norm_add: h must be contiguous float32 and a of its shape; h={tuple(h.shape)} a={tuple(a.shape)}")
+    stride = 0
+    if history is not None:
+        if (history.dtype != torch.float32 or history.dim() != 3 or history.shape[1:] != h.shape or not history.is_contiguous()
+                or not 0 <= n_prev < history.shape[0] or coef is None or coef.numel() < n_prev + 1 or not coef.is_contiguous()):
+            raise KernelError("branch_norm_add: history must be contiguous float32 [slots, rows, hidden] with coef [n_prev + 1]")
+        stride = history.stride(0)
+    _lib.check(_lib.load().oi_branch_norm_add(h.data_ptr(), a.data_ptr(), _code(a, "branch_norm_add"), weight.data_ptr(),
+                                              _code(weight, "branch_norm_add weight"), rows, hidden, float(eps),
+                                              float(weight_offset), _ptr(history), stride, int(n_prev), _ptr(coef),
+                                              0 if coef is None else _code(coef, "branch_norm_add coef"), _ptr(low), _stream()),
+               "branch_norm_add")
+    return h
+
+
+def history_average(h: torch.Tensor, history: torch.Tensor, n_prev: int, coef: torch.Tensor) -> torch.Tensor:
+    """history[n_prev] = h; h <- sum_{j <= n_prev} coef[j] history[j] (all float32, h in place)."""
+    _cuda(h, history, coef)
+    if (h.dtype != torch.float32 or history.dtype != torch.float32 or history.shape[1:] != h.shape or not h.is_contiguous()
+            or not history.is_contiguous() or not 0 <= n_prev < history.shape[0] or coef.numel() < n_prev + 1):
+        raise KernelError("history_average: h and history must be contiguous float32, history [slots, *h.shape]")
+    _lib.check(_lib.load().oi_history_average(h.data_ptr(), history.data_ptr(), history.stride(0), int(n_prev), coef.data_ptr(),
+                                              _code(coef, "history_average coef"), h.numel(), _stream()), "history_average")
+    return h
+
+
+def short_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor],
+               cu_seqlens: torch.Tensor, token_req: torch.Tensor, state_slots: torch.Tensor, *, add_input: bool = True,
+               update_state: bool = True) -> torch.Tensor:
+    """Causal convolution over time on each channel, per request of a flattened step:
+    out[t] = (x[t] if add_input) + sum_j weight[:, j] * x_(t - taps + 1 + j). ``state`` float32 [slots, taps - 1,
+    channels] holds every request's last taps - 1 inputs (zeros before its start); with ``update_state`` it is
+    moved on by this step's rows afterwards. x float32 or the type of out."""
+    _cuda(out, x, weight, state, cu_seqlens, token_req, state_slots)
+    for t, what in ((cu_seqlens, "cu_seqlens"), (token_req, "token_req"), (state_slots, "state_slots")):
+        _i32(t, f"short_conv {what}")
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    if out.shape != x.shape or weight.shape[0] != channels or not (out.is_contiguous() and x.is_contiguous() and weight.is_contiguous()):
+        raise KernelError(f"short_conv: shapes x={tuple(x.shape)} out={tuple(out.shape)} weight={tuple(weight.shape)}")
+    stride = 0
+    if taps > 1:
+        if state is None or state.dtype != torch.float32 or state.shape[1:] != (taps - 1, channels) or not state.is_contiguous():
+            raise KernelError(f"short_conv: {taps} taps need a contiguous float32 state [slots, {taps - 1}, {channels}]")
+        stride = state.stride(0)
+    requests = cu_seqlens.numel() - 1
+    _lib.check(_lib.load().oi_short_conv(out.data_ptr(), _code(out, "short_conv"), x.data_ptr(), _code(x, "short_conv"),
+                                         weight.data_ptr(), _code(weight, "short_conv weight"), _ptr(state), stride,
+                                         cu_seqlens.data_ptr(), token_req.data_ptr(), state_slots.data_ptr(), tokens, requests,
+                                         channels, taps, 1 if add_input else 0, 1 if update_state else 0, _stream()), "short_conv")
+    return out
+
+
+def latent_store(pages: torch.Tensor, page_stride: int, src: torch.Tensor, weight: torch.Tensor, slots: torch.Tensor,
+                 rank: int, eps: float, weight_offset: float = 0.0) -> None:
+    """RMS norm of src[t, :rank] (row stride free) with ``weight`` and the write of the result to the row's slot
+    of ``pages`` [pages, page_size, 1, row_elems >= rank] (elements beyond rank are zeroed; slot < 0: no write)."""
+    _cuda(pages, src, weight, slots)
+    _i32(slots, "latent_store slots")
+    if pages.dtype != src.dtype or src.stride(1) != 1 or src.shape[1] < rank or weight.numel() != rank or slots.numel() != src.shape[0]:
+        raise KernelError(f"latent_store: src={tuple(src.shape)} pages={tuple(pages.shape)} rank={rank}")
+    _lib.check(_lib.load().oi_latent_store(pages.data_ptr(), int(page_stride), pages.shape[1], pages.shape[-1], src.data_ptr(),
+                                           src.stride(0), _code(src, "latent_store"), weight.data_ptr(),
+                                           _code(weight, "latent_store weight"), slots.data_ptr(), src.shape[0], int(rank),
+                                           float(eps), float(weight_offset), _stream()), "latent_store")
+
+
+def head_gate(o: torch.Tensor, g: torch.Tensor, heads: int, head_elems: int) -> torch.Tensor:
+    """o[t, h, :] *= sigmoid(g[t, h]) in place; o [tokens, >= heads * head_elems], g [tokens, >= heads], row strides free."""
+    _cuda(o, g)
+    if o.dtype != g.dtype or o.stride(1) != 1 or g.stride(1) != 1 or o.shape[0] != g.shape[0] or o.shape[1] < heads * head_elems \
+            or g.shape[1] < heads:
+        raise KernelError(f"head_gate: o={tuple(o.shape)} g={tuple(g.shape)} heads={heads} head_elems={head_elems}")
+    _lib.check(_lib.load().oi_head_gate(o.data_ptr(), o.stride(0), g.data_ptr(), g.stride(0), _code(o, "head_gate"), o.shape[0],
+                                        int(heads), int(head_elems), _stream()), "head_gate")
+    return o
+
+
+def xielu(out: torch.Tensor, x: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """out = a_p x^2 + x / 2 for x > 0, a_n (exp(x) - 1 - x) + x / 2 otherwise, with a_p = softplus(pq[0]) and
+    a_n = 1/2 + softplus(pq[1]) formed on the device."""
+    _cuda(out, x, pq)
+    if out.dtype != x.dtype or out.shape != x.shape or not (out.is_contiguous() and x.is_contiguous()) or pq.numel() != 2:
+        raise KernelError("xielu: out and x must be contiguous and alike, pq two numbers")
+    _lib.check(_lib.load().oi_xielu(out.data_ptr(), x.data_ptr(), _code(x, "xielu"), pq.data_ptr(), _code(pq, "xielu pq"),
+                                    x.numel(), _stream()), "xielu")
+    return out

@@ -111,3 +111,13 @@ class Block(Part):
     @property
     def mixer(self) -> Optional[Mixer]:
         return None
+
+    # the type of the stream the block works on: None = the model's own
+    stream_dtype: Optional[torch.dtype] = None
+    # the block's result is kept for later blocks (``ctx.scratch["stream_history"]``: [tensor, results so far])
+    wants_history = False
+
+    def state_needs(self) -> List[StateNeed]:
+        """Per-request state of the block's parts, in the order of ``CacheBinding.states``."""
+        m = self.mixer
+        return m.state_needs() if m is not None else []

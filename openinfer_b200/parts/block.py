@@ -4,12 +4,15 @@ the norm that follows it (the reference fuses the same way: flashinfer_norm.cu:3
 pegainfer-qwen3/src/batch_decode.rs:210-236)."""
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, Optional, Tuple
 
 import torch
 
+from ..kernels import ops
 from .base import Block, CacheBinding, Part
-from .registry import build_feed_forward, build_mixer, build_norm, register_block
+from .norm import RmsNorm
+from .registry import build_feed_forward, build_mixer, build_norm, build_stream_part, register_block
 from .spec import BlockSpec
 
 
@@ -42,3 +45,90 @@ class PreNormBlock(Block):
         x = self.post_norm(h, delta=a)                 # h += a; x = norm(h)
         m = self.feed_forward.forward(x, ctx)
         return h, m
+
+
+@register_block("branchnorm")
+class BranchNormBlock(Block):
+    """x <- x + norm(mixer(f(x))), then x <- x + norm(ff(x)): the norms sit on the branches' OUTPUTS and the branches
+    read the stream itself. f is an optional filter over time (``input_conv``: f(x) = x + conv(x)); the feed-forward is
+    optional; with ``depth_average`` the block's result X is kept and the stream that goes on is a weighted sum of the
+    results of all blocks so far and of the embedding output.
+
+    The stream is float32 whatever the model's type: the branches get it rounded to the model's type (by the filter, or
+    by the kernel that ends the branch before), return float32, and one kernel norms a branch's output, adds it, and,
+    after the block's last branch, forms the average. ``spec.input_norm`` is the norm of the mixer's output,
+    ``spec.post_norm`` that of the feed-forward's.
+    """
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__(spec)
+        self._mixer = build_mixer(spec.mixer)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.mixer_norm = build_norm(spec.input_norm)
+        self.ff_norm = build_norm(spec.post_norm) if spec.feed_forward is not None else None
+        self.conv = build_stream_part(spec.input_conv) if spec.input_conv is not None else None
+        self.depth = build_stream_part(spec.depth_average) if spec.depth_average is not None else None
+        for n in (self.mixer_norm, self.ff_norm):
+            if n is not None and not isinstance(n, RmsNorm):
+                raise ValueError("a branchnorm block needs rms norms")
+
+    wants_history = property(lambda self: self.depth is not None)
+    stream_dtype = torch.float32
+
+    @property
+    def mixer(self):
+        return self._mixer
+
+    def sub_parts(self) -> Dict[str, Part]:
+        s = self.spec
+        parts: Dict[str, Part] = {s.input_norm_name: self.mixer_norm, s.mixer_name: self._mixer}
+        if self.feed_forward is not None:
+            parts[s.post_norm_name] = self.ff_norm
+            parts[s.feed_forward_name] = self.feed_forward
+        if self.conv is not None:
+            parts[s.input_conv_name] = self.conv
+        if self.depth is not None:
+            parts[s.depth_average_name] = self.depth
+        return parts
+
+    def state_needs(self):
+        return (self.conv.state_needs() if self.conv is not None else []) + self._mixer.state_needs()
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx,
+                binding: CacheBinding) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if h.dtype != torch.float32 or pending is not None:
+            raise RuntimeError("a branchnorm block takes a float32 stream with no branch pending")
+        dtype = ctx.scratch["model_dtype"]
+        n_conv = len(self.conv.state_needs()) if self.conv is not None else 0
+        if self.conv is not None:
+            u = self.conv.forward(h, ctx, binding.states[:n_conv], dtype)
+        else:
+            u = ctx.scratch.pop("stream_low", None)
+            if u is None:
+                u = h if dtype == torch.float32 else h.to(dtype)
+        ctx.scratch.pop("stream_low", None)
+        wide = {"out_dtype": torch.float32}      # parts that can, hand their branch back unrounded
+        a = self._mixer.forward(u, ctx, dataclasses.replace(binding, states=binding.states[n_conv:]),
+                                **(wide if getattr(self._mixer, "takes_out_dtype", False) else {}))
+        hist = ctx.scratch.get("stream_history") if self.depth is not None else None
+        low = torch.empty(h.shape, dtype=dtype, device=h.device) if dtype != torch.float32 else None
+
+        def join(branch, norm, last, low_out):
+            kw = {}
+            if last and hist is not None:
+                kw = dict(history=hist[0], n_prev=hist[1], coef=self.depth.weight)
+                if self.depth.weight.numel() != hist[1] + 1:
+                    raise RuntimeError(f"depth average: {self.depth.weight.numel()} weights for {hist[1] + 1} terms")
+                hist[1] += 1
+            ops.branch_norm_add(h, branch, norm.weight, norm.spec.eps, weight_offset=norm.spec.weight_offset, low=low_out, **kw)
+
+        if self.feed_forward is None:
+            join(a, self.mixer_norm, True, low)
+        else:
+            join(a, self.mixer_norm, False, low)
+            m = self.feed_forward.forward(low if low is not None else h, ctx,
+                                          **(wide if getattr(self.feed_forward, "takes_out_dtype", False) else {}))
+            join(m, self.ff_norm, True, low)
+        if low is not None:
+            ctx.scratch["stream_low"] = low      # the stream as it goes on, rounded: what the next block's branch reads
+        return h, None

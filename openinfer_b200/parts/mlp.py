@@ -71,3 +71,40 @@ class GatedMlp(FeedForward):
                                   codes[self.w_down.dtype], self.act_code, self.block, act.data_ptr(), 0 if gate_up is None else gate_up.data_ptr(),
                                   _lib.current_stream()), "gated_mlp")
         return out
+
+
+@register_feed_forward("dense_mlp")
+class DenseMlp(FeedForward):
+    """down( act(up x) ) with one up-projection; "xielu" is a quadratic above zero and an exponential below it,
+    a_p z^2 + z / 2 and a_n (e^z - 1 - z) + z / 2, whose a_p = softplus(p) and a_n = 1/2 + softplus(q) come from a tensor
+    of two numbers and are formed on the device in float32."""
+
+    takes_out_dtype = True
+
+    def __init__(self, spec) -> None:
+        super().__init__(spec)
+        if spec.activation != "xielu":
+            raise ops.KernelError(f"activation {spec.activation!r} has no kernel for a dense feed-forward (known: xielu)")
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+        self.act: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s = self.spec
+        return {
+            s.up_name: ParamInfo((s.intermediate_size, s.hidden_size), ("normal", s.hidden_size ** -0.5)),
+            s.down_name: ParamInfo((s.hidden_size, s.intermediate_size), ("normal", s.intermediate_size ** -0.5)),
+            s.act_name: ParamInfo((2,), ("normal", 0.5)),
+        }
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.w_up = tensors[s.up_name].contiguous()
+        self.w_down = tensors[s.down_name].contiguous()
+        self.act = tensors[s.act_name].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        from ..kernels.linear import linear
+        z = linear(x, self.w_up)
+        ops.xielu(z, z, self.act)
+        return linear(z, self.w_down, out_dtype=out_dtype)

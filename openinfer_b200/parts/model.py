@@ -100,11 +100,27 @@ class Model:
     # ------------------------------------------------------------------ cache
     def bind_cache(self, cache: CacheManager) -> None:
         """Register what every entry of the run order needs from the cache manager."""
-        self.bindings = []
-        for c in self.calls:
+        import dataclasses as _dc
+
+        # An entry whose pages other entries read keeps them as long as the longest window among its readers needs
+        # them (for ever, if one of them has no window): pages are given back by the group's window.
+        needs = {}
+        for i, c in enumerate(self.calls):
             mixer = self.blocks[c.layer].mixer
+            need = mixer.kv_need() if mixer is not None else None
+            if c.read_cache_of is None:
+                needs[i] = need
+            elif need is not None and needs.get(c.read_cache_of) is not None:
+                src = needs[c.read_cache_of]
+                if src.window is not None and (need.window is None or need.window > src.window):
+                    needs[c.read_cache_of] = _dc.replace(src, window=need.window)
+        self.bindings = []
+        for i, c in enumerate(self.calls):
+            block = self.blocks[c.layer]
+            mixer = block.mixer
+            states = tuple(cache.add_state(n) for n in block.state_needs())
             if mixer is None:
-                self.bindings.append(CacheBinding())
+                self.bindings.append(CacheBinding(states=states))
                 continue
             if c.read_cache_of is not None:
                 src = self.bindings[c.read_cache_of]
@@ -112,23 +128,33 @@ class Model:
                     raise ValueError("run order entry reads the cache of an entry without keys and values")
                 src_need = self.blocks[self.calls[c.read_cache_of].layer].mixer.kv_need()
                 need = mixer.kv_need()
-                if need is None or (need.num_kv_heads, need.head_dim) != (src_need.num_kv_heads, src_need.head_dim):
+                if need is None or (need.num_kv_heads, need.head_dim, need.planes) != (src_need.num_kv_heads, src_need.head_dim,
+                                                                                       src_need.planes):
                     raise ValueError("a layer can only read the cache of a layer with the same kv heads and head size")
                 kv, owns = src.kv, False
             else:
-                need = mixer.kv_need()
+                need = needs[i]
                 kv, owns = (cache.add_kv_layer(need) if need is not None else None), True
-            states = tuple(cache.add_state(n) for n in mixer.state_needs())
             self.bindings.append(CacheBinding(kv=kv, owns_kv=owns, states=states))
 
     # ------------------------------------------------------------------ forward
+    def stream_dtype(self) -> torch.dtype:
+        return torch.float32 if self.spec.residual_dtype == "float32" else self.dtype
+
     def forward(self, ctx) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Run all rows of the step through the blocks. Returns the residual stream as
         (h, pending): pending is the last branch output, not yet added."""
-        h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=self.dtype, device=self.device)
+        h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=self.stream_dtype(), device=self.device)
         ops.embedding(h, self.embedding, ctx.token_ids)
         if self.spec.embedding_scale != 1.0:
             ops.scale_cap(h, scale=self.spec.embedding_scale)
+        ctx.scratch["model_dtype"] = self.dtype
+        ctx.scratch.pop("stream_low", None)
+        if any(self.blocks[c.layer].wants_history for c in self.calls):
+            # the embedding output and every block's result, for blocks that average over them
+            history = torch.empty((len(self.calls) + 1, ctx.num_tokens, self.spec.hidden_size), dtype=h.dtype, device=self.device)
+            history[0].copy_(h)
+            ctx.scratch["stream_history"] = [history, 1]
         pending = None
         for call, binding in zip(self.calls, self.bindings):
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, binding)
@@ -269,8 +295,11 @@ class Model:
     def logits(self, h: torch.Tensor, pending: Optional[torch.Tensor], row_idx: torch.Tensor) -> torch.Tensor:
         """Float32 logits [rows, vocab] of the wanted rows only: gather + final norm in one
         kernel, then the head (pegainfer-qwen3/src/prefill.rs:440-477)."""
-        x = self.final_norm(h, delta=pending, row_idx=row_idx)
+        if h.dtype != self.dtype:
+            x = self.final_norm(h, delta=pending, row_idx=row_idx, out_dtype=self.dtype)
+        else:
+            x = self.final_norm(h, delta=pending, row_idx=row_idx)
         out = linear(x, self.head, out_dtype=torch.float32)
-        if self.spec.logit_soft_cap > 0.0:
-            ops.scale_cap(out, cap=self.spec.logit_soft_cap)
+        if self.spec.logit_soft_cap > 0.0 or self.spec.logit_scale != 1.0:
+            ops.scale_cap(out, scale=self.spec.logit_scale, cap=self.spec.logit_soft_cap)
         return out

@@ -23,14 +23,19 @@ class RmsNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamInfo]:
-        return {"weight": ParamInfo((self.spec.size,), ("one_plus_normal", 0.02))}
+        return {self.spec.param_name: ParamInfo((self.spec.size,), ("one_plus_normal", 0.02))}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.spec.param_name].contiguous()
 
     def __call__(self, x: torch.Tensor, *, delta: Optional[torch.Tensor] = None,
-                 row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 row_idx: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         rows = x.shape[0] if row_idx is None else row_idx.numel()
+        if out_dtype is not None and out_dtype != x.dtype:      # a 32-bit stream normed into the model's type
+            if delta is not None:
+                raise ValueError("a norm that changes the type takes no pending branch")
+            out = torch.empty((rows, x.shape[1]), dtype=out_dtype, device=x.device)
+            return ops.rmsnorm_cast(out, x, self.weight, self.spec.eps, row_idx=row_idx, weight_offset=self.spec.weight_offset)
         out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
         return ops.rmsnorm(out, x, self.weight, self.spec.eps, delta=delta, row_idx=row_idx,
                            weight_offset=self.spec.weight_offset)

@@ -14,6 +14,7 @@ FEED_FORWARDS: Dict[str, Callable[[Any], Any]] = {}
 NORMS: Dict[str, Callable[[Any], Any]] = {}
 POSITION_ENCODINGS: Dict[str, Callable[[Any], Any]] = {}
 BLOCKS: Dict[str, Callable[[Any], Any]] = {}
+STREAM_PARTS: Dict[str, Callable[[Any], Any]] = {}    # parts that act on the residual stream itself (filters, averages)
 
 
 def _register(table: Dict[str, Any], what: str):
@@ -31,6 +32,7 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_block = _register(BLOCKS, "block")
+register_stream_part = _register(STREAM_PARTS, "stream part")
 
 
 def _build(table: Dict[str, Any], what: str, spec: Any):
@@ -54,6 +56,10 @@ def build_norm(spec):
 
 def build_position_encoding(spec):
     return _build(POSITION_ENCODINGS, "position encoding", spec)
+
+
+def build_stream_part(spec):
+    return _build(STREAM_PARTS, "stream part", spec)
 
 
 def build_block(spec):

@@ -17,12 +17,12 @@ from typing import Any, List, Optional, Tuple, Union
 class ParamInfo:
     """One tensor a part wants from the checkpoint.
 
-    ``init`` is how the random-weights mode draws it: ("normal", std) or
-    ("one_plus_normal", std). ``integer`` tensors are kept as int32.
+    ``init`` is how the random-weights mode draws it: ("normal", std),
+    ("one_plus_normal", std) or ("normal_around", std, mean). ``integer`` tensors are kept as int32.
     """
 
     shape: Tuple[int, ...]
-    init: Tuple[str, float] = ("normal", 0.02)
+    init: Tuple = ("normal", 0.02)
     integer: bool = False
 
 
@@ -32,6 +32,7 @@ class NormSpec:
     size: int = 0
     eps: float = 1e-6
     weight_offset: float = 0.0  # scale is (weight_offset + w)
+    param_name: str = "weight"  # local tensor name (appended to the prefix the enclosing part gives the norm)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -59,6 +60,68 @@ class AttentionSpec:
 
 
 @dataclasses.dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention over a low-rank latent: one vector c of ``latent_rank`` numbers per position is cached, and every head
+    forms its keys and values from it (k = Wuk_h c, v = Wuv_h c). No position encoding."""
+
+    kind: str = "latent_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    qk_dim: int = 0                         # per head: size of queries and keys
+    v_dim: int = 0                          # per head: size of values
+    latent_rank: int = 0
+    softmax_scale: float = 0.0
+    latent_norm: Optional[NormSpec] = None  # norm of the latent before it is cached and used
+    window: Optional[int] = None            # keys visible to a query, itself included; None = all
+    output_gate: bool = False               # head h's output is multiplied by sigmoid(Wg x)_h
+    has_latent: bool = True                 # False: the layer reads the latent of an earlier layer and has no down-projection
+    # how the per-head up-projections are applied: "weights" multiplies them into the query and output projections
+    # once at load time; "runtime" applies them to the queries and to the attention's output in every step
+    absorb: str = "weights"
+    q_name: str = "q"
+    down_name: str = "dkv"
+    latent_norm_name: str = "dkv.norm"
+    up_k_name: str = "uk"
+    up_v_name: str = "uv"
+    gate_name: str = "g"
+    out_name: str = "o"
+
+
+@dataclasses.dataclass(frozen=True)
+class DenseMlpSpec:
+    """down( act(up x) ) with one up-projection. ``activation`` "xielu": the two shape numbers are a tensor."""
+
+    kind: str = "dense_mlp"
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "xielu"
+    up_name: str = "up"
+    down_name: str = "down"
+    act_name: str = "act"
+
+
+@dataclasses.dataclass(frozen=True)
+class ShortConvSpec:
+    """Causal convolution over time on each channel; the last ``taps - 1`` inputs are per-request state."""
+
+    kind: str = "short_conv"
+    channels: int = 0
+    taps: int = 0
+    add_input: bool = True                  # out = x + conv(x) rather than conv(x)
+    param_name: str = ""
+
+
+@dataclasses.dataclass(frozen=True)
+class DepthAverageSpec:
+    """After a layer, the stream becomes a weighted sum of the outputs of all layers so far (and of the embedding
+    output): ``terms`` weights, one tensor."""
+
+    kind: str = "depth_average"
+    terms: int = 0
+    param_name: str = ""
+
+
+@dataclasses.dataclass(frozen=True)
 class GatedMlpSpec:
     kind: str = "gated_mlp"
     hidden_size: int = 0
@@ -80,6 +143,10 @@ class BlockSpec:
     feed_forward_name: str = "mlp."
     input_norm_name: str = "input_layernorm."
     post_norm_name: str = "post_attention_layernorm."
+    input_conv: Any = None                       # blocks that filter the mixer's input over time (ShortConvSpec)
+    input_conv_name: str = "conv."
+    depth_average: Any = None                    # blocks whose result is averaged with earlier layers' (DepthAverageSpec)
+    depth_average_name: str = "depth."
 
 
 @dataclasses.dataclass(frozen=True)
@@ -108,6 +175,8 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     embedding_scale: float = 1.0     # the embedded rows are multiplied by this (1: as stored, the reference's Qwen3)
     logit_soft_cap: float = 0.0      # > 0: logits = cap * tanh(logits / cap)
+    logit_scale: float = 1.0         # the logits are multiplied by this
+    residual_dtype: str = "model"    # "model": the stream between layers has the model's type; "float32": always 32-bit
 
     def calls(self) -> List[LayerCall]:
         return [c if isinstance(c, LayerCall) else LayerCall(int(c)) for c in self.order]

@@ -1,0 +1,64 @@
+"""Parts that act on the residual stream itself rather than on a branch of it.
+
+"short_conv": a causal convolution over time on every channel, out = x + conv(x) (or conv(x) alone), whose last
+``taps - 1`` inputs per request are state kept in the cache manager's slots, so a portion of a prompt or a single
+decoded token continues where the request's earlier steps ended.
+
+"depth_average": after a layer, the stream becomes a weighted sum of the outputs of all layers so far and of the
+embedding output. It owns only the weights; the sum itself is formed by the kernel that ends the layer's last branch
+(``ops.branch_norm_add``) or by ``ops.history_average``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache.manager import StateNeed
+from ..kernels import ops
+from .base import Part
+from .registry import register_stream_part
+from .spec import DepthAverageSpec, ParamInfo, ShortConvSpec
+
+
+@register_stream_part("short_conv")
+class ShortConv(Part):
+    def __init__(self, spec: ShortConvSpec) -> None:
+        super().__init__(spec)
+        if spec.taps < 1 or spec.channels <= 0:
+            raise ValueError(f"short_conv needs taps >= 1 and channels > 0, got {spec.taps} and {spec.channels}")
+        self.weight: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s = self.spec
+        return {s.param_name: ParamInfo((s.channels, s.taps), ("normal", 0.3))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.spec.param_name].contiguous()
+
+    def state_needs(self) -> List[StateNeed]:
+        s = self.spec
+        return [StateNeed((s.taps - 1, s.channels), "float32")] if s.taps > 1 else []
+
+    def forward(self, x: torch.Tensor, ctx, state_ids, out_dtype: torch.dtype) -> torch.Tensor:
+        """x [tokens, channels] (float32 or ``out_dtype``) -> x + conv(x) in ``out_dtype``; the state moves on."""
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        state = ctx.cache.state_tensor(state_ids[0]) if self.spec.taps > 1 else None
+        return ops.short_conv(out, x, self.weight, state, ctx.cu_seqlens, ctx.token_req, ctx.state_slots,
+                              add_input=self.spec.add_input)
+
+
+@register_stream_part("depth_average")
+class DepthAverage(Part):
+    def __init__(self, spec: DepthAverageSpec) -> None:
+        super().__init__(spec)
+        if spec.terms < 1:
+            raise ValueError("depth_average needs at least one term")
+        self.weight: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s = self.spec
+        return {s.param_name: ParamInfo((s.terms,), ("normal_around", 0.2, 1.0 / s.terms))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.spec.param_name].contiguous()

@@ -2,7 +2,8 @@
 
 Each tensor is drawn from its own generator, seeded from (seed, tensor name), so a
 tensor's values do not depend on which other tensors exist. Matrices are N(0, std),
-norm weights 1 + N(0, std), drawn in float32 and rounded once to the stored dtype.
+norm weights 1 + N(0, std), other vectors N(mean, std) as their part says, drawn in
+float32 and rounded once to the stored dtype.
 The reference has no random-weights mode (its tests need real checkpoints); this is
 what makes tiny and full-size models available without any download.
 """
@@ -34,10 +35,12 @@ def random_tensors(expected: Dict[str, ParamInfo], seed: int, dtype: torch.dtype
         if info.integer:
             out[name] = torch.randint(0, 2, info.shape, generator=gen, device=device, dtype=torch.int32)
             continue
-        kind, std = info.init
+        kind, std = info.init[0], info.init[1]
         t = torch.randn(info.shape, generator=gen, device=device, dtype=torch.float32) * std
         if kind == "one_plus_normal":
             t = t + 1.0
+        elif kind == "normal_around":      # ("normal_around", std, mean)
+            t = t + float(info.init[2])
         elif kind != "normal":
             raise ValueError(f"{name}: unknown init {kind!r}")
         out[name] = t.to(dtype)
