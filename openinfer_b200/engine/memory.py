@@ -21,8 +21,8 @@ def pages_from_memory_budget(config, weights_seed, folder, dtype, device, page_s
     if not (0.0 < utilization <= 1.0):
         raise ValueError(f"gpu_memory_utilization must be in (0, 1], got {utilization}")
     tdtype = _dtype_of(dtype)
-    probe_tokens = max(1, min(max_prefill_tokens, config.max_position_embeddings
-                              if hasattr(config, "max_position_embeddings") else max_prefill_tokens))
+    # a config without a position limit (none, or 0) is probed with a whole prompt portion
+    probe_tokens = max(1, min(max_prefill_tokens, getattr(config, "max_position_embeddings", 0) or max_prefill_tokens))
     probe_pages = -(-probe_tokens // page_size) + 1
     runner = ModelRunner.build(config, weights_seed, dtype=dtype, device=device, page_size=page_size,
                                num_pages=probe_pages, max_requests=8, folder=folder, strict_weights=strict_weights)
