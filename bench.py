@@ -400,6 +400,200 @@ def measure_size(torch, mods, key, args, peaks, mixed: bool):
     return flat, rec
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design delunex: the Delunex design at layer sizes of real models, beside Qwen3 at equal sizes
+# ---------------------------------------------------------------------------------------------------------------
+# name -> (width, layers, heads, window, Delunex ff, Qwen3 intermediate size): per head 128 query/key, value and
+# latent numbers; the two feed-forwards hold the same number of weights (2 x ff = 3 x intermediate).
+DESIGN_SIZES = {
+    "1k": (1024, 16, 16, 1024, 4608, 3072),
+    "2k": (2048, 24, 16, 1024, 9216, 6144),
+    "4k": (4096, 32, 32, 2048, 18432, 12288),
+}
+DESIGN_VOCAB = 32768
+
+
+def design_configs(key, layers=None):
+    width, n_layers, heads, window, ff, inter = DESIGN_SIZES[key]
+    n_layers = layers or n_layers
+    mixer = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 128, "scale": 128 ** -0.5, "mask": {"size": window}}
+    # as in small models of this design: two of every three layers read the latent of the layer before them
+    lay = []
+    for i in range(n_layers):
+        m = dict(mixer)
+        if i % 3:
+            m["kv_from"] = i - i % 3
+        lay.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    delunex = {"architecture": "Delunex", "vocab": DESIGN_VOCAB, "width": width, "logit_scale": 1.0,
+               "embedding": {"scale": float(width) ** 0.5}, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "layers": lay}
+    qwen = dict(QWEN3_8B, num_hidden_layers=n_layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), intermediate_size=inter, vocab_size=DESIGN_VOCAB,
+                tie_word_embeddings=True, max_position_embeddings=1 << 20)
+    return delunex, qwen
+
+
+class DesignBench:
+    """One model (any registered architecture) on the GPU with requests whose contexts are filled, not computed."""
+
+    def __init__(self, torch, mods, cfg_dict, dtype, context, max_batch, room):
+        self.torch, self.mods, self.context = torch, mods, context
+        self.config = mods["resolve_architecture"](cfg_dict).config_cls.from_dict(cfg_dict)
+        self.dev = torch.device("cuda:0")
+        per_req = context + room + 2 * PAGE
+        self.runner = mods["ModelRunner"].build(self.config, 0, dtype=dtype, device=self.dev, page_size=PAGE,
+                                                max_tokens=max_batch * per_req + PREFILL_TOKENS + 64, max_requests=max_batch + 4)
+        self.runner.cuda_graph = True
+        for g in self.runner.cache.groups:
+            g.tensor.normal_(0.0, 0.5)
+        self.rng = random.Random(0)
+        self.vocab = self.runner.spec.vocab_size
+        self.esize = 2 if dtype == "bfloat16" else 4
+
+    def close(self):
+        import gc
+        self.runner = None
+        gc.collect()
+        self.torch.cuda.synchronize()
+        self.torch.cuda.empty_cache()
+
+    def _open(self, ids):
+        cache = self.runner.cache
+        for rid in ids:
+            cache.open(rid)
+            cache.reserve(rid, self.context)
+            cache.commit(rid)
+
+    def decode(self, batch, steps, warmup, profile=False):
+        torch, runner, ops, StepEntry = self.torch, self.runner, self.mods["ops"], self.mods["StepEntry"]
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        self._open(ids)
+        toks = [[self.rng.randrange(self.vocab)] for _ in ids]
+        out = torch.empty(batch, dtype=torch.int32, device=self.dev)
+
+        def one():
+            ops.argmax(out, runner.step([StepEntry(rid, t, [0]) for rid, t in zip(ids, toks)]))
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        kernels = kernel_times(torch, one, 3) if profile else None
+        l0 = self.mods["klib"].launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        launches = self.mods["klib"].launch_count() - l0
+        for rid in ids:
+            runner.end(rid)
+        return e0.elapsed_time(e1) / steps, launches, kernels
+
+    def prefill(self, T, reps=3, warm=3, profile=False):
+        torch, runner, StepEntry = self.torch, self.runner, self.mods["StepEntry"]
+        toks = [self.rng.randrange(self.vocab) for _ in range(T)]
+        times, n = [], [0]
+
+        def one():
+            n[0] += 1
+            runner.step([StepEntry(f"pf{n[0]}", toks, [T - 1])])
+            runner.end(f"pf{n[0]}")
+
+        for i in range(warm + reps):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            one()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(e0.elapsed_time(e1))
+        return statistics.median(times), (kernel_times(torch, one, 2) if profile else None)
+
+    # what the step has to move and to compute, from the assembled model itself
+    def decode_bytes(self, batch):
+        total = self.runner.model.weight_bytes()
+        for call, binding in zip(self.runner.model.calls, self.runner.model.bindings):
+            need = self.runner.model.blocks[call.layer].mixer.kv_need()
+            keys = min(self.context, need.window) if need.window else self.context
+            total += batch * keys * need.planes * need.num_kv_heads * need.head_dim * self.esize
+        return total
+
+    def prefill_flops(self, T):
+        model = self.runner.model
+        flops = 0.0
+        for call in model.calls:
+            block = model.blocks[call.layer]
+            for part in block.sub_parts().values():
+                for v in vars(part).values():
+                    if isinstance(v, self.torch.Tensor) and v.dim() == 2 and v.shape[0] > 2 and v.shape[1] > 8:
+                        flops += 2.0 * T * v.shape[0] * v.shape[1]
+            need = block.mixer.kv_need()
+            spec = block.mixer.spec
+            heads = spec.num_heads
+            seen = sum(min(t + 1, need.window) if need.window else t + 1 for t in range(T))
+            flops += 4.0 * heads * need.head_dim * seen
+        return flops + 2.0 * self.vocab * model.spec.hidden_size
+
+
+def kernel_times(torch, one, steps):
+    """name -> (launches per step, microseconds per step) of the GPU kernels of `steps` calls of `one` (CUPTI through
+    torch.profiler; kernels overlap under programmatic dependent launch, so the times add up to more than the step)."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            one()
+        torch.cuda.synchronize()
+    acc = {}
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0][:48]
+            n, us = acc.get(name, (0, 0.0))
+            acc[name] = (n + 1, us + (e.time_range.end - e.time_range.start))
+    return {k: (round(n / steps, 1), round(us / steps, 1)) for k, (n, us) in sorted(acc.items(), key=lambda kv: -kv[1][1])}
+
+
+def design_mode(args, torch, mods, peaks, peaks_src):
+    """Delunex and Qwen3 at equal layer sizes: decode at batch 1 / 8 / 64 and a 2,048-token prefill, device-timed,
+    with roofline fractions, and (--design-kernels) the kernels of a batch-8 decode step and of the prefill."""
+    sizes = [x for x in (args.design_sizes or "1k,2k").split(",") if x]
+    steps, warm = max(16, args.steps // 2), max(3, args.warmup)
+    out = {"design": args.design, "dtype": args.dtype, "context": CONTEXT, "data": "synthetic (random weights, filled caches)",
+           "peaks": peaks, "peaks_source": peaks_src, "sizes": {}}
+    sampler = ClockSampler(0)
+    sampler.start()
+    try:
+        for key in sizes:
+            if key not in DESIGN_SIZES:
+                raise SystemExit(f"--design-sizes: unknown size {key!r} (known: {', '.join(DESIGN_SIZES)})")
+            rec = {"width": DESIGN_SIZES[key][0], "layers": args.layers or DESIGN_SIZES[key][1]}
+            for arch, cfg in zip((args.design, "qwen3"), design_configs(key, args.layers)):
+                b = DesignBench(torch, mods, cfg, args.dtype, CONTEXT, 64, steps + warm + 16)
+                r = {"weights_gb": round(b.runner.model.weight_bytes() / 1e9, 3)}
+                for batch in (1, 8, 64):
+                    ms, launches, kern = b.decode(batch, steps, warm, profile=args.design_kernels and batch == 8)
+                    r[f"decode_b{batch}_tok_s"] = round(batch * 1000.0 / ms, 1)
+                    r[f"decode_b{batch}_ms"] = round(ms, 4)
+                    r[f"decode_b{batch}_hbm_frac"] = round(b.decode_bytes(batch) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                    if batch == 8:
+                        r["decode_b8_launches_per_step"] = round(launches / steps, 1)
+                        if kern:
+                            r["decode_b8_kernels"] = kern
+                ms, kern = b.prefill(PREFILL_TOKENS, profile=args.design_kernels)
+                r[f"prefill_{PREFILL_TOKENS}_tok_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+                r[f"prefill_{PREFILL_TOKENS}_ms"] = round(ms, 3)
+                r[f"prefill_{PREFILL_TOKENS}_frac"] = round(b.prefill_flops(PREFILL_TOKENS) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+                if kern:
+                    r["prefill_kernels"] = kern
+                rec[arch] = r
+                b.close()
+            out["sizes"][key] = rec
+    finally:
+        out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     global CONTEXT
     ap = argparse.ArgumentParser()
@@ -433,6 +627,15 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
+    ap.add_argument("--design", default=None, choices=["delunex"],
+                    help="instead of the headline workload: this design at layer sizes of real models beside Qwen3 at equal "
+                         "sizes (decode at batch 1/8/64, a 2,048-token prefill), one JSON line")
+    ap.add_argument("--design-sizes", default=None, help="sizes for --design, comma separated (1k, 2k, 4k; default 1k,2k)")
+    ap.add_argument("--design-kernels", action="store_true",
+                    help="with --design: also every kernel's launches and microseconds per step (decode at batch 8, prefill)")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="launch kernels without programmatic dependent launch (a kernel's time then holds no waiting "
+                         "for its predecessor: for per-kernel figures, not for throughput)")
     args = ap.parse_args()
     CONTEXT = args.context
 
@@ -464,6 +667,10 @@ def main() -> int:
     if args.sampler or args.profile == "sampler":
         return sampler_mode(args, torch, ops, MODELS[args.model][1]["vocab_size"])
     peaks, peaks_src = read_peaks()
+    if args.no_pdl:
+        klib.load().oi_set_pdl(0)
+    if args.design:
+        return design_mode(args, torch, mods, peaks, peaks_src)
     model_name, model_cfg = MODELS[args.model]
     K, W, B = args.steps, args.warmup, args.batch
     headline_full = args.model == "8b" and not args.layers and args.dtype == "bfloat16" and not args.batch_invariant

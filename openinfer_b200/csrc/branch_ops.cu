@@ -192,6 +192,226 @@ __global__ void xielu_kernel(T* out, const T* in, const void* __restrict__ pq, i
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same steps moving 16 bytes (or four elements) per access, for rows and pointers that allow it. A thread
+// keeps its part of the row in registers between the sum of squares and the output.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load4(const float* p, float v[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float v[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+  v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+}
+__device__ __forceinline__ void load4(const void* p, int dtype, size_t i, float v[4]) {
+  if (dtype == OI_F32) load4(reinterpret_cast<const float*>(p) + i, v);
+  else load4(reinterpret_cast<const bf16*>(p) + i, v);
+}
+__device__ __forceinline__ void store4(float* p, const float v[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(bf16* p, const float v[4]) {
+  uint2 t;
+  *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+constexpr int kMaxCoef = 256;   // terms of an average the vector kernel keeps in shared memory
+
+template <typename TA, int VPT>
+__global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const TA* __restrict__ a, const void* __restrict__ w, int w_dtype,
+                                           int hidden, float eps, float w_offset, float* __restrict__ hist, long long hist_stride,
+                                           int n_prev, const void* __restrict__ coef, int coef_dtype, bf16* __restrict__ low) {
+  pdl_trigger();
+  __shared__ float red[32];
+  __shared__ float cf[kMaxCoef];
+  const int nvec = hidden / 4;
+  float wv[VPT][4];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {     // weights and coefficients do not depend on the kernels ahead on the stream
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) load4(w, w_dtype, (size_t)v * 4, wv[k]);
+  }
+  if (hist != nullptr)
+    for (int j = threadIdx.x; j <= n_prev; j += blockDim.x) cf[j] = load_as_f32(coef, coef_dtype, j);
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * hidden;
+  float av[VPT][4], hv[VPT][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      load4(a + row + (size_t)v * 4, av[k]);
+      load4(h + row + (size_t)v * 4, hv[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += av[k][e] * av[k][e];
+    }
+  }
+  ss = block_sum(ss, red);      // its barriers also publish cf
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v >= nvec) continue;
+    const size_t at = row + (size_t)v * 4;
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = hv[k][e] + av[k][e] * inv * (w_offset + wv[k][e]);
+    if (hist != nullptr) {
+      store4(hist + (size_t)n_prev * hist_stride + at, x);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int j = 0; j < n_prev; ++j) {
+        float p[4];
+        load4(hist + (size_t)j * hist_stride + at, p);
+        const float c = cf[j];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += c * p[e];
+      }
+      const float c = cf[n_prev];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = acc[e] + c * x[e];
+    }
+    store4(h + at, x);
+    if (low != nullptr) store4(low + at, x);
+  }
+}
+
+// kConvRows consecutive rows and four channels per thread: a row's earlier inputs stay in registers while the thread
+// walks down its rows (rows of one request are consecutive), the taps' weights are read once, and only a request's
+// first rows of the step go to its state
+constexpr int kConvRows = 4;
+constexpr int kConvMaxTaps = 8;
+template <typename TX, typename TO, int kTaps>     // kTaps: 2, 4 or 8, at least the taps
+__global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                                      const float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
+                                      const int* __restrict__ token_req, const int* __restrict__ state_slots, int tokens,
+                                      int channels, int taps, int add_input) {
+  pdl_trigger();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const int t0 = blockIdx.x * kConvRows;
+  const int keep = taps - 1;
+  float wt[kTaps][4];
+  if (c < channels) {
+#pragma unroll
+    for (int j = 0; j < kTaps; ++j)
+      if (j < taps) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wt[j][e] = load_as_f32(w, w_dtype, (size_t)(c + e) * taps + keep - j);   // of the input j rows above
+      }
+  }
+  pdl_wait();
+  if (c >= channels) return;
+  // ring[(row - 1 - i) mod taps]: the input i + 1 rows above the current one
+  float ring[kTaps][4];
+#pragma unroll
+  for (int j = 0; j < kTaps; ++j) {
+    const int r = t0 - 1 - j;
+    if (j < keep && r >= 0) load4(x + (size_t)r * channels + c, ring[j]);
+  }
+  const int t_end = min(tokens, t0 + kConvRows);
+  // the requests of the rows and of the taps - 1 rows above them, and the rows' inputs: all asked for before any is used.
+  // A request's rows are consecutive, so a row's place in its portion shows in its neighbours' requests alone.
+  int reqs[kConvRows + kTaps - 1];
+  float curs[kConvRows][4];
+#pragma unroll
+  for (int i = 0; i < kConvRows + kTaps - 1; ++i) {
+    const int r = t0 - (kTaps - 1) + i;
+    reqs[i] = (r >= 0 && r < t_end && r >= t0 - keep) ? token_req[r] : -2;
+  }
+#pragma unroll
+  for (int i = 0; i < kConvRows; ++i)
+    if (t0 + i < t_end) load4(x + (size_t)(t0 + i) * channels + c, curs[i]);
+#pragma unroll
+  for (int i = 0; i < kConvRows; ++i) {
+    const int t = t0 + i;
+    if (t >= t_end) break;
+    const int req = reqs[i + kTaps - 1];
+    int rel = 0;                 // rows of the same request directly above, up to taps - 1
+#pragma unroll
+    for (int j = 1; j < kTaps; ++j)
+      if (j <= keep && rel == j - 1 && reqs[i + kTaps - 1 - j] == req) rel = j;
+    const float* st = (req >= 0 && rel < keep) ? state + (size_t)state_slots[req] * state_stride : nullptr;
+    float cur[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cur[e] = curs[i][e];
+    float acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = add_input ? cur[e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < kTaps; ++j) {     // tap keep - j reads the input j rows above (j = 0: the row itself)
+      if (j >= taps) break;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (j == 0) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = cur[e];
+      } else if (rel - j >= 0) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = ring[j - 1][e];
+      } else if (st) {
+        load4(st + (size_t)(keep + rel - j) * channels + c, v);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] += wt[j][e] * v[e];
+    }
+    store4(out + (size_t)t * channels + c, acc);
+#pragma unroll
+    for (int j = kTaps - 1; j > 0; --j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ring[j][e] = ring[j - 1][e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ring[0][e] = cur[e];
+  }
+}
+
+// o[t, h, :] *= sigmoid(g[t, h]), 16 bytes per access (a head's elements are a multiple of the vector)
+template <typename T>
+__global__ void head_gate_vec_kernel(T* __restrict__ o, long long o_stride, const T* __restrict__ g, long long g_stride,
+                                     int head_elems, int vecs_per_row) {
+  pdl_start();
+  constexpr int EPV = 16 / sizeof(T);
+  const int t = blockIdx.x;
+  for (int v = blockIdx.y * blockDim.x + threadIdx.x; v < vecs_per_row; v += gridDim.y * blockDim.x) {
+    const float gate = sigmoid_f(to_f32(g[(size_t)t * g_stride + (v * EPV) / head_elems]));
+    T* p = o + (size_t)t * o_stride + (size_t)v * EPV;
+    float a[4], b[4] = {0.f, 0.f, 0.f, 0.f};
+    load4(p, a);
+    if (EPV == 8) load4(p + 4, b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[e] *= gate, b[e] *= gate;
+    store4(p, a);
+    if (EPV == 8) store4(p + 4, b);
+  }
+}
+
+// 16 bytes per access
+template <typename T>
+__global__ void xielu_vec_kernel(T* out, const T* in, const void* __restrict__ pq, int pq_dtype, long long nvec) {
+  pdl_start();
+  constexpr int EPV = 16 / sizeof(T);
+  const float ap = softplus_f(load_as_f32(pq, pq_dtype, 0));
+  const float an = 0.5f + softplus_f(load_as_f32(pq, pq_dtype, 1));
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float z[8];
+    load4(in + i * EPV, z);
+    if (EPV == 8) load4(in + i * EPV + 4, z + 4);
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) {
+      // a bfloat16 result keeps 8 bits: the special-function unit's exponential (2 ulp of float32) is exact enough there
+      const float em1 = sizeof(T) == 2 ? __expf(z[e]) - 1.f : expm1f(z[e]);
+      z[e] = z[e] > 0.f ? ap * z[e] * z[e] + 0.5f * z[e] : an * (em1 - z[e]) + 0.5f * z[e];
+    }
+    store4(out + i * EPV, z);
+    if (EPV == 8) store4(out + i * EPV + 4, z + 4);
+  }
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 int flat_blocks(long long n) {
   const long long b = (n + kRowThreads - 1) / kRowThreads;
   return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b));
@@ -227,6 +447,23 @@ OI_API int oi_branch_norm_add(float* h, const void* a, int a_dtype, const void* 
              "branch_norm_add: the history needs coefficients and a stride of at least rows * hidden");
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  const int nvec = hidden / 4;
+  if (hidden % 4 == 0 && nvec <= 512 * 4 && aligned16(h) && aligned16(a) && aligned16(w) && (!hist || (aligned16(hist) && hist_stride % 4 == 0 &&
+      n_prev < kMaxCoef)) && (!low || aligned16(low)) && (a_dtype == OI_F32 || a_dtype == OI_BF16)) {
+    const int vpt = nvec <= 256 ? 1 : (nvec <= 1024 ? 2 : 4);
+    const int threads = (((nvec + vpt - 1) / vpt + 31) / 32) * 32;
+#define OI_BNA(TA, V)                                                                                                        \
+  oi_launch(branch_norm_add_vec_kernel<TA, V>, rows, threads, 0, s, h, (const TA*)a, w, w_dtype, hidden, eps, w_offset, hist, \
+            hist_stride, n_prev, coef, coef_dtype, (bf16*)low)
+    if (a_dtype == OI_F32) {
+      if (vpt == 1) OI_BNA(float, 1); else if (vpt == 2) OI_BNA(float, 2); else OI_BNA(float, 4);
+    } else {
+      if (vpt == 1) OI_BNA(bf16, 1); else if (vpt == 2) OI_BNA(bf16, 2); else OI_BNA(bf16, 4);
+    }
+#undef OI_BNA
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   if (a_dtype == OI_F32)
     oi_launch(branch_norm_add_kernel<float>, rows, kRowThreads, 0, s, h, (const float*)a, w, w_dtype, hidden, eps, w_offset, hist,
               hist_stride, n_prev, coef, coef_dtype, (bf16*)low);
@@ -260,8 +497,22 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
   cudaStream_t s = (cudaStream_t)stream;
   const int cy = (channels + kRowThreads - 1) / kRowThreads;
   const dim3 grid(tokens, cy);
+  const bool vec = channels % 4 == 0 && taps <= kConvMaxTaps && aligned16(out) && aligned16(x) &&
+                   (taps == 1 || (aligned16(state) && state_stride % 4 == 0));
+  const int vthreads = channels / 4 >= 256 ? 256 : ((channels / 4 + 31) / 32) * 32;
+  const dim3 vgrid((tokens + kConvRows - 1) / kConvRows, vec ? (channels / 4 + vthreads - 1) / vthreads : 1);
 #define OI_CONV_CASE(XD, OD, TX, TO)                                                                                     \
   if (x_dtype == XD && out_dtype == OD) {                                                                                \
+    if (vec && taps <= 2)                                                                                                \
+      oi_launch(short_conv_vec_kernel<TX, TO, 2>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
+                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
+    else if (vec && taps <= 4)                                                                                           \
+      oi_launch(short_conv_vec_kernel<TX, TO, 4>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
+                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
+    else if (vec)                                                                                                        \
+      oi_launch(short_conv_vec_kernel<TX, TO, 8>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
+                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
+    else                                                                                                                 \
     oi_launch(short_conv_kernel<TX, TO>, grid, kRowThreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, (const float*)state, \
               state_stride, cu_seqlens, token_req, state_slots, channels, taps, add_input);                              \
     OI_CHECK_LAUNCH();                                                                                                   \
@@ -304,6 +555,18 @@ OI_API int oi_head_gate(void* o, long long o_stride, const void* g, long long g_
   const long long n = (long long)tokens * heads * head_elems;
   if (n == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  const int epv = dtype == OI_F32 ? 4 : 8;
+  if ((dtype == OI_F32 || dtype == OI_BF16) && head_elems % epv == 0 && o_stride % epv == 0 && aligned16(o)) {
+    const int vecs = heads * head_elems / epv;
+    const int threads = vecs >= 256 ? 256 : ((vecs + 31) / 32) * 32;
+    const dim3 grid(tokens, (vecs + threads - 1) / threads);
+    if (dtype == OI_F32)
+      oi_launch(head_gate_vec_kernel<float>, grid, threads, 0, s, (float*)o, o_stride, (const float*)g, g_stride, head_elems, vecs);
+    else
+      oi_launch(head_gate_vec_kernel<bf16>, grid, threads, 0, s, (bf16*)o, o_stride, (const bf16*)g, g_stride, head_elems, vecs);
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   if (dtype == OI_F32)
     oi_launch(head_gate_kernel<float>, flat_blocks(n), kRowThreads, 0, s, (float*)o, o_stride, (const float*)g, g_stride, heads,
               head_elems, n);
@@ -320,6 +583,15 @@ OI_API int oi_xielu(void* out, const void* in, int dtype, const void* pq, int pq
   OI_REQUIRE(n >= 0 && pq != nullptr, "xielu: bad arguments");
   if (n == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  const int epv = dtype == OI_F32 ? 4 : 8;
+  if ((dtype == OI_F32 || dtype == OI_BF16) && n % epv == 0 && aligned16(out) && aligned16(in)) {
+    if (dtype == OI_F32)
+      oi_launch(xielu_vec_kernel<float>, flat_blocks(n / epv), kRowThreads, 0, s, (float*)out, (const float*)in, pq, pq_dtype, n / epv);
+    else
+      oi_launch(xielu_vec_kernel<bf16>, flat_blocks(n / epv), kRowThreads, 0, s, (bf16*)out, (const bf16*)in, pq, pq_dtype, n / epv);
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   if (dtype == OI_F32)
     oi_launch(xielu_kernel<float>, flat_blocks(n), kRowThreads, 0, s, (float*)out, (const float*)in, pq, pq_dtype, n);
   else if (dtype == OI_BF16)

@@ -335,3 +335,79 @@ OI_API int oi_forward(const OiModelDesc* m, const OiStepDesc* st, void* stream) 
   }
   return OI_OK;
 }
+
+OI_API int oi_forward_branch(const OiBranchModelDesc* m, const OiBranchStepDesc* st, void* stream) {
+  OI_REQUIRE(m && st && m->layers && (st->num_attn_steps == 0 || st->attn_steps), "forward_branch: null description");
+  const int T = st->tokens, H = m->hidden, dt = m->dtype;
+  OI_REQUIRE(T >= 0 && H > 0, "forward_branch: bad sizes tokens=%d hidden=%d", T, H);
+  if (T == 0) return OI_OK;
+  OI_REQUIRE(dt == OI_F32 || st->low, "forward_branch: a bfloat16 model needs the rounded copy of the stream");
+  const long long hist_stride = (long long)T * H;
+  OI_TRY(oi_embedding(st->h, OI_F32, m->embedding, m->embedding_dtype, st->token_ids, T, H, m->vocab, stream));
+  if (m->embedding_scale != 1.f) OI_TRY(oi_scale_cap(st->h, OI_F32, (long long)T * H, m->embedding_scale, 0.f, stream));
+  int results = 0;             // entries of the history so far
+  if (st->hist) {
+    OI_CHECK_CUDA(cudaMemcpyAsync(st->hist, st->h, sizeof(float) * (size_t)T * H, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    results = 1;
+  }
+  bool low_valid = false;      // `low` holds the stream as it stands
+  for (int i = 0; i < m->num_layers; ++i) {
+    const OiBranchLayerDesc& L = m->layers[i];
+    OI_REQUIRE(L.attn_step >= 0 && L.attn_step < st->num_attn_steps, "forward_branch: layer %d names attention step %d of %d", i,
+               L.attn_step, st->num_attn_steps);
+    // ---- what the mixer reads
+    const void* u = st->u;
+    if (L.conv_w) {
+      OI_TRY(oi_short_conv(st->u, dt, st->h, OI_F32, L.conv_w, L.conv_w_dtype, L.conv_state, L.conv_state_stride, st->cu_seqlens,
+                           st->token_req, st->state_slots, T, st->requests, H, L.taps, L.add_input, 1, stream));
+    } else if (dt == OI_F32) {
+      u = st->h;
+    } else {
+      OI_REQUIRE(low_valid, "forward_branch: layer %d has no filter and nothing has rounded the stream yet", i);
+      u = st->low;
+    }
+    // ---- queries | latent | gate, the latent's norm and page write, attention over the latent, the gate, the output
+    OI_TRY(oi_linear(st->proj, dt, L.in_cols, u, dt, H, L.w_in, L.w_in_dtype, H, T, L.in_cols, H, stream));
+    const size_t esize = dt == OI_F32 ? 4 : 2;
+    const OiAttnStep& as = st->attn_steps[L.attn_step];
+    if (L.latent_norm_w)
+      OI_TRY(oi_latent_store(L.pages, as.page_stride, as.page_size, L.row, (const char*)st->proj + esize * L.latent_off, L.in_cols, dt,
+                             L.latent_norm_w, L.latent_norm_dtype, as.slot_mapping, T, L.rank, L.latent_eps, L.latent_offset, stream));
+    OiAttnLayer a = {};
+    a.qkv = st->proj, a.out = st->mixed, a.k_cache = L.pages, a.v_cache = L.pages;
+    a.q_row_stride = L.in_cols, a.out_row_stride = L.heads * L.row, a.dtype = dt;
+    a.nq = L.heads, a.nkv = 1, a.hd = L.row, a.window = L.window, a.scale = L.scale;
+    a.write_kv = 0, a.rope_mode = 0;
+    OI_TRY(oi_attention_layer(&as, &a, stream));
+    if (L.has_gate)
+      OI_TRY(oi_head_gate(st->mixed, L.heads * L.row, (const char*)st->proj + esize * L.gate_off, L.in_cols, dt, T, L.heads, L.row, stream));
+    OI_TRY(oi_linear(st->branch, OI_F32, H, st->mixed, dt, L.heads * L.row, L.w_out, L.w_out_dtype, L.heads * L.row, T, H,
+                     L.heads * L.row, stream));
+    // ---- the branches join the stream; the layer's last one also forms the average
+    const bool averaged = L.depth_coef != nullptr;
+    OI_REQUIRE(!averaged || (st->hist && L.depth_terms == results + 1), "forward_branch: layer %d averages %d terms, %d exist", i,
+               L.depth_terms, results + 1);
+    const bool has_ff = L.w_up != nullptr;
+    OI_TRY(oi_branch_norm_add(st->h, st->branch, OI_F32, L.mixer_norm_w, L.mixer_norm_dtype, T, H, L.mixer_eps, L.mixer_offset,
+                              (!has_ff && averaged) ? st->hist : nullptr, hist_stride, results, L.depth_coef, L.depth_dtype,
+                              st->low, stream));
+    if (has_ff) {
+      OI_TRY(oi_linear(st->z, dt, L.inter, dt == OI_F32 ? (const void*)st->h : st->low, dt, H, L.w_up, L.w_up_dtype, H, T, L.inter, H, stream));
+      OI_TRY(oi_xielu(st->z, st->z, dt, L.act_pq, L.pq_dtype, (long long)T * L.inter, stream));
+      OI_TRY(oi_linear(st->branch, OI_F32, H, st->z, dt, L.inter, L.w_down, L.w_down_dtype, L.inter, T, H, L.inter, stream));
+      OI_TRY(oi_branch_norm_add(st->h, st->branch, OI_F32, L.ff_norm_w, L.ff_norm_dtype, T, H, L.ff_eps, L.ff_offset,
+                                averaged ? st->hist : nullptr, hist_stride, results, L.depth_coef, L.depth_dtype, st->low, stream));
+    }
+    if (averaged) ++results;
+    low_valid = st->low != nullptr;
+  }
+  if (st->num_want > 0) {
+    OI_REQUIRE(st->want_rows && st->wanted && st->logits, "forward_branch: wanted rows without buffers");
+    OI_TRY(oi_rmsnorm_cast(st->wanted, dt, st->h, OI_F32, m->final_norm_w, m->final_norm_dtype, st->want_rows, st->num_want, H,
+                           m->final_eps, m->final_offset, stream));
+    OI_TRY(oi_linear(st->logits, OI_F32, m->vocab, st->wanted, dt, H, m->head, m->head_dtype, H, st->num_want, m->vocab, H, stream));
+    if (m->logit_soft_cap > 0.f || m->logit_scale != 1.f)
+      OI_TRY(oi_scale_cap(st->logits, OI_F32, (long long)st->num_want * m->vocab, m->logit_scale, m->logit_soft_cap, stream));
+  }
+  return OI_OK;
+}

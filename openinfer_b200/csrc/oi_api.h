@@ -282,3 +282,62 @@ typedef struct OiStepDesc {
 
 // Embedding, every layer, final norm of the wanted rows, head: all kernels of one step, launched from native code.
 OI_API int oi_forward(const OiModelDesc* model, const OiStepDesc* step, void* stream);
+
+// ------------------------------------------------------------------------------------------------
+// The same for models whose every layer is a "branchnorm" block over a float32 stream (branch_ops.cu): an
+// optional short convolution in front of the mixer, attention over a cached latent (up-projections multiplied
+// into the weights), the norm on each branch's output fused with the residual sum, an optional dense
+// feed-forward, an optional weighted average over the results of all layers so far.
+// ------------------------------------------------------------------------------------------------
+typedef struct OiBranchLayerDesc {
+  const void* conv_w;         // [hidden, taps] or null: the mixer then reads the stream as it is
+  float* conv_state;          // [slots, taps - 1, hidden] or null (one tap)
+  const void* w_in;           // [in_cols, hidden]: queries | latent | gate | zero rows
+  const void* w_out;          // [hidden, heads * row]
+  const void* latent_norm_w;  // [rank] or null (the layer reads another layer's latent)
+  void* pages;                // the latent's pages [pages, page_size, 1, row]
+  const void* mixer_norm_w;   // [hidden]
+  const void* ff_norm_w;      // [hidden] or null
+  const void* w_up;           // [inter, hidden] or null (no feed-forward)
+  const void* w_down;         // [hidden, inter]
+  const void* act_pq;         // the activation's two numbers
+  const void* depth_coef;     // [depth_terms] or null
+  long long conv_state_stride;
+  int conv_w_dtype, taps, add_input;
+  int w_in_dtype, w_out_dtype, latent_norm_dtype, mixer_norm_dtype, ff_norm_dtype, w_up_dtype, w_down_dtype, pq_dtype, depth_dtype;
+  int in_cols, heads, row, rank, window, latent_off, gate_off, has_gate;
+  int attn_step, inter, depth_terms;
+  float scale, latent_eps, latent_offset, mixer_eps, mixer_offset, ff_eps, ff_offset;
+} OiBranchLayerDesc;
+
+typedef struct OiBranchModelDesc {
+  const OiBranchLayerDesc* layers;   // host pointer, num_layers entries in run order
+  const void* embedding;
+  const void* final_norm_w;
+  const void* head;
+  int num_layers, hidden, vocab, dtype;
+  int embedding_dtype, final_norm_dtype, head_dtype;
+  float embedding_scale, final_eps, final_offset, logit_soft_cap, logit_scale;
+} OiBranchModelDesc;
+
+typedef struct OiBranchStepDesc {
+  const int* token_ids;
+  const OiAttnStep* attn_steps;      // host pointer
+  const int* want_rows;
+  const int* cu_seqlens;
+  const int* token_req;
+  const int* state_slots;
+  float* h;                   // [tokens, hidden] the stream
+  float* hist;                // [num_layers + 1, tokens, hidden] or null (no layer averages)
+  void* u;                    // [tokens, hidden] what the mixer reads, in the model's type
+  void* low;                  // [tokens, hidden] the stream rounded to the model's type (bfloat16 models; else null)
+  void* proj;                 // [tokens, max in_cols]
+  void* mixed;                // [tokens, max heads * row]
+  float* branch;              // [tokens, hidden]
+  void* z;                    // [tokens, max inter]
+  void* wanted;               // [num_want, hidden]
+  float* logits;              // [num_want, vocab]
+  int tokens, requests, num_attn_steps, num_want;
+} OiBranchStepDesc;
+
+OI_API int oi_forward_branch(const OiBranchModelDesc* model, const OiBranchStepDesc* step, void* stream);

@@ -89,6 +89,43 @@ class StepDesc(Structure):
     ]
 
 
+class BranchLayerDesc(Structure):
+    _fields_ = [
+        ("conv_w", c_void_p), ("conv_state", c_void_p), ("w_in", c_void_p), ("w_out", c_void_p), ("latent_norm_w", c_void_p),
+        ("pages", c_void_p), ("mixer_norm_w", c_void_p), ("ff_norm_w", c_void_p), ("w_up", c_void_p), ("w_down", c_void_p),
+        ("act_pq", c_void_p), ("depth_coef", c_void_p),
+        ("conv_state_stride", c_longlong),
+        ("conv_w_dtype", c_int), ("taps", c_int), ("add_input", c_int),
+        ("w_in_dtype", c_int), ("w_out_dtype", c_int), ("latent_norm_dtype", c_int), ("mixer_norm_dtype", c_int),
+        ("ff_norm_dtype", c_int), ("w_up_dtype", c_int), ("w_down_dtype", c_int), ("pq_dtype", c_int), ("depth_dtype", c_int),
+        ("in_cols", c_int), ("heads", c_int), ("row", c_int), ("rank", c_int), ("window", c_int), ("latent_off", c_int),
+        ("gate_off", c_int), ("has_gate", c_int),
+        ("attn_step", c_int), ("inter", c_int), ("depth_terms", c_int),
+        ("scale", c_float), ("latent_eps", c_float), ("latent_offset", c_float), ("mixer_eps", c_float), ("mixer_offset", c_float),
+        ("ff_eps", c_float), ("ff_offset", c_float),
+    ]
+
+
+class BranchModelDesc(Structure):
+    _fields_ = [
+        ("layers", POINTER(BranchLayerDesc)), ("embedding", c_void_p), ("final_norm_w", c_void_p), ("head", c_void_p),
+        ("num_layers", c_int), ("hidden", c_int), ("vocab", c_int), ("dtype", c_int),
+        ("embedding_dtype", c_int), ("final_norm_dtype", c_int), ("head_dtype", c_int),
+        ("embedding_scale", c_float), ("final_eps", c_float), ("final_offset", c_float), ("logit_soft_cap", c_float),
+        ("logit_scale", c_float),
+    ]
+
+
+class BranchStepDesc(Structure):
+    _fields_ = [
+        ("token_ids", c_void_p), ("attn_steps", POINTER(AttnStep)), ("want_rows", c_void_p), ("cu_seqlens", c_void_p),
+        ("token_req", c_void_p), ("state_slots", c_void_p),
+        ("h", c_void_p), ("hist", c_void_p), ("u", c_void_p), ("low", c_void_p), ("proj", c_void_p), ("mixed", c_void_p),
+        ("branch", c_void_p), ("z", c_void_p), ("wanted", c_void_p), ("logits", c_void_p),
+        ("tokens", c_int), ("requests", c_int), ("num_attn_steps", c_int), ("num_want", c_int),
+    ]
+
+
 def declare(lib) -> None:
     """Argument types of the host-step entry points (called by ``lib.load``)."""
     P, I, L = c_void_p, c_int, c_longlong
@@ -103,6 +140,7 @@ def declare(lib) -> None:
     lib.oi_gated_mlp_needs_gate_up.argtypes, lib.oi_gated_mlp_needs_gate_up.restype = [I, I, I, I, I, I], c_int
     lib.oi_attention_layer.argtypes, lib.oi_attention_layer.restype = [POINTER(AttnStep), POINTER(AttnLayer), P], c_int
     lib.oi_forward.argtypes, lib.oi_forward.restype = [POINTER(ModelDesc), POINTER(StepDesc), P], c_int
+    lib.oi_forward_branch.argtypes, lib.oi_forward_branch.restype = [POINTER(BranchModelDesc), POINTER(BranchStepDesc), P], c_int
     lib.oi_launches.argtypes, lib.oi_launches.restype = [], ctypes.c_ulonglong
     lib.oi_launch_fence.argtypes, lib.oi_launch_fence.restype = [], c_int
     lib.oi_gemm_stream_fused.argtypes = [P, I, L, P, L, P, L, I, I, I, I, I, POINTER(StreamEpilogue), P]

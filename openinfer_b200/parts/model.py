@@ -183,6 +183,10 @@ class Model:
         def own(obj, cls):
             return type(obj) is cls
 
+        from .block import BranchNormBlock
+        if own(self.final_norm, RmsNorm) and all(own(b, BranchNormBlock) for b in self.blocks):
+            self._native = self._native_description_branch(ctx)
+            return self._native
         if not own(self.final_norm, RmsNorm) or not all(
                 own(b, PreNormBlock) and own(b.mixer, Attention) and own(b.feed_forward, GatedMlp)
                 and own(b.input_norm, RmsNorm) and own(b.post_norm, RmsNorm) for b in self.blocks):
@@ -240,7 +244,124 @@ class Model:
         self._native = (desc, keys, reps)
         return self._native
 
+    def _native_description_branch(self, ctx):
+        """The model as ``oi_forward_branch`` sees it (csrc/oi_api.h, OiBranchModelDesc), or None when a block has a part
+        that entry point does not know (then the parts are called one by one)."""
+        from .latent_attention import LatentAttention
+        from .mlp import DenseMlp
+        from .norm import RmsNorm
+        from .stream import DepthAverage, ShortConv
+
+        def own(obj, cls):
+            return type(obj) is cls
+
+        for i, b in enumerate(self.blocks):
+            ok = (own(b.mixer, LatentAttention) and b.mixer.spec.absorb == "weights" and own(b.mixer_norm, RmsNorm)
+                  and (b.feed_forward is None or (own(b.feed_forward, DenseMlp) and own(b.ff_norm, RmsNorm)))
+                  and (b.conv is None or own(b.conv, ShortConv)) and (b.depth is None or own(b.depth, DepthAverage)))
+            if not ok or (b.conv is None and self.dtype != torch.float32 and i == 0):
+                return None
+        codes = native.DTYPE_CODE
+        cache = ctx.cache
+        layers = (native.BranchLayerDesc * len(self.calls))()
+        keys: List[tuple] = []
+        reps: List[int] = []
+        for i, (call, binding) in enumerate(zip(self.calls, self.bindings)):
+            b = self.blocks[call.layer]
+            at, s = b.mixer, b.mixer.spec
+            pages, _, _ = cache.kv_views(binding.kv)
+            key = (binding.kv.group, s.num_heads, at.row, s.window, at.in_cols)
+            if key not in keys:
+                keys.append(key)
+                reps.append(i)
+            L = layers[i]
+            n_conv = 0
+            if b.conv is not None:
+                cs = b.conv.spec
+                L.conv_w, L.conv_w_dtype, L.taps, L.add_input = b.conv.weight.data_ptr(), codes[b.conv.weight.dtype], cs.taps, int(cs.add_input)
+                if cs.taps > 1:
+                    state = cache.state_tensor(binding.states[0])
+                    L.conv_state, L.conv_state_stride = state.data_ptr(), state.stride(0)
+                    n_conv = 1
+            L.w_in, L.w_in_dtype, L.in_cols = at.w_in.data_ptr(), codes[at.w_in.dtype], at.in_cols
+            L.w_out, L.w_out_dtype = at.w_out.data_ptr(), codes[at.w_out.dtype]
+            if s.has_latent:
+                L.latent_norm_w, L.latent_norm_dtype = at.w_latent_norm.data_ptr(), codes[at.w_latent_norm.dtype]
+                L.latent_eps, L.latent_offset = s.latent_norm.eps, s.latent_norm.weight_offset
+            L.pages = pages.data_ptr()
+            L.heads, L.row, L.rank, L.window = s.num_heads, at.row, s.latent_rank, int(s.window) if s.window else 0
+            L.latent_off, L.gate_off, L.has_gate, L.scale = at.latent_off, at.gate_off, int(s.output_gate), s.softmax_scale
+            L.attn_step = keys.index(key)
+            mn = b.mixer_norm
+            L.mixer_norm_w, L.mixer_norm_dtype, L.mixer_eps, L.mixer_offset = mn.weight.data_ptr(), codes[mn.weight.dtype], mn.spec.eps, mn.spec.weight_offset
+            if b.feed_forward is not None:
+                ff, fn = b.feed_forward, b.ff_norm
+                L.ff_norm_w, L.ff_norm_dtype, L.ff_eps, L.ff_offset = fn.weight.data_ptr(), codes[fn.weight.dtype], fn.spec.eps, fn.spec.weight_offset
+                L.w_up, L.w_up_dtype, L.w_down, L.w_down_dtype = ff.w_up.data_ptr(), codes[ff.w_up.dtype], ff.w_down.data_ptr(), codes[ff.w_down.dtype]
+                L.act_pq, L.pq_dtype, L.inter = ff.act.data_ptr(), codes[ff.act.dtype], ff.spec.intermediate_size
+            if b.depth is not None:
+                L.depth_coef, L.depth_dtype, L.depth_terms = b.depth.weight.data_ptr(), codes[b.depth.weight.dtype], b.depth.weight.numel()
+        sp = self.spec
+        desc = native.BranchModelDesc(
+            layers=layers, embedding=self.embedding.data_ptr(), final_norm_w=self.final_norm.weight.data_ptr(),
+            head=self.head.data_ptr(), num_layers=len(self.calls), hidden=sp.hidden_size, vocab=sp.vocab_size,
+            dtype=codes[self.dtype], embedding_dtype=codes[self.embedding.dtype],
+            final_norm_dtype=codes[self.final_norm.weight.dtype], head_dtype=codes[self.head.dtype],
+            embedding_scale=sp.embedding_scale, final_eps=self.final_norm.spec.eps,
+            final_offset=self.final_norm.spec.weight_offset, logit_soft_cap=sp.logit_soft_cap, logit_scale=sp.logit_scale)
+        desc.keep = layers
+        desc.max_in = max(L.in_cols for L in layers)
+        desc.max_mixed = max(L.heads * L.row for L in layers)
+        desc.max_inter = max([L.inter for L in layers] + [1])
+        desc.averaged = any(L.depth_terms for L in layers)
+        return ("branch", desc, keys, reps)
+
+    def _run_native_branch(self, native_desc, ctx, row_idx: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        _, desc, keys, reps = native_desc
+        T, H, dev, dt = ctx.num_tokens, self.spec.hidden_size, self.device, self.dtype
+        lib = _lib.load()
+        if T > 32:
+            ensure_library(dev)
+
+        def buf(cols, dtype=dt, rows=T):
+            return torch.empty((rows, cols), dtype=dtype, device=dev)
+
+        f32 = torch.float32
+        h, branch, u = buf(H, f32), buf(H, f32), buf(H)
+        low = buf(H) if dt != f32 else None
+        hist = torch.empty((len(self.calls) + 1, T, H), dtype=f32, device=dev) if desc.averaged else None
+        proj, mixed, z = buf(desc.max_in), buf(desc.max_mixed), buf(desc.max_inter)
+        steps = (native.AttnStep * len(keys))()
+        kept = []
+        for j, (key, i) in enumerate(zip(keys, reps)):
+            call, binding = self.calls[i], self.bindings[i]
+            at = self.blocks[call.layer].mixer
+            pages, _, page_stride = ctx.cache.kv_views(binding.kv)
+            L = desc.keep[i]
+            s = attn_kernels.attention_step(ctx, ctx.groups[binding.kv.group], proj.view(-1)[: T * L.in_cols].view(T, L.in_cols),
+                                            mixed.view(-1)[: T * L.heads * L.row].view(T, L.heads * L.row), pages, page_stride,
+                                            L.heads, 1, L.row, at.spec.window)
+            kept.append(s)
+            ctypes.memmove(ctypes.byref(steps[j]), ctypes.byref(s), ctypes.sizeof(native.AttnStep))
+        n_want = 0 if row_idx is None else row_idx.numel()
+        wanted = buf(H, rows=n_want) if n_want else None
+        logits = buf(self.spec.vocab_size, dtype=f32, rows=n_want) if n_want else None
+
+        def ptr(t):
+            return 0 if t is None else t.data_ptr()
+
+        step = native.BranchStepDesc(
+            token_ids=ctx.token_ids.data_ptr(), attn_steps=steps, want_rows=ptr(row_idx) if n_want else 0,
+            cu_seqlens=ctx.cu_seqlens.data_ptr(), token_req=ctx.token_req.data_ptr(), state_slots=ctx.state_slots.data_ptr(),
+            h=h.data_ptr(), hist=ptr(hist), u=u.data_ptr(), low=ptr(low), proj=proj.data_ptr(), mixed=mixed.data_ptr(),
+            branch=branch.data_ptr(), z=z.data_ptr(), wanted=ptr(wanted), logits=ptr(logits), tokens=T, requests=ctx.num_requests,
+            num_attn_steps=len(keys), num_want=n_want)
+        _lib.check(lib.oi_forward_branch(ctypes.byref(desc), ctypes.byref(step), _lib.current_stream()), "forward_branch")
+        return logits
+
     def _run_native(self, native_desc, ctx, row_idx: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if native_desc[0] == "branch":
+            return self._run_native_branch(native_desc, ctx, row_idx)
         desc, keys, reps = native_desc
         T, H, dev, dt = ctx.num_tokens, self.spec.hidden_size, self.device, self.dtype
         lib = _lib.load()

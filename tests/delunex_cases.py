@@ -72,7 +72,19 @@ CASE_E = {
     "norm": {"eps": 1e-4},
     "layers": [_layer(2, 16, 16, 24, 1.0, window=9, ff=64), _layer(2, 16, 16, 24, 1.0, window=9)],
 }
-CASES = {"A": (CASE_A, 11), "B": (CASE_B, 12), "C": (CASE_C, 13), "D": (CASE_D, 14), "E": (CASE_E, 15)}
+# sizes that are multiples of nothing: no vector load, tensor-core tile or copy unit applies as it stands
+CASE_F = {
+    "architecture": "Delunex", "vocab": 101, "width": 100, "logit_scale": 0.9, "embedding": {"scale": 2.0},
+    "norm": {"eps": 1e-6}, "canon": {"taps": 3},
+    "layers": [_layer(3, 12, 20, 20, 1.0, window=19, ff=50), _layer(5, 4, 6, 20, 1.0, window=70, kv_from=0, ff=30)],
+}
+CASE_G = {
+    "architecture": "Delunex", "vocab": 99, "width": 36, "logit_scale": 1.1, "embedding": {"scale": 2.0},
+    "norm": {"eps": 1e-6}, "canon": {"taps": 2},
+    "layers": [_layer(7, 5, 3, 9, 1.0, window=5, ff=21), _layer(1, 2, 2, 9, 1.0, kv_from=0)],
+}
+CASES = {"A": (CASE_A, 11), "B": (CASE_B, 12), "C": (CASE_C, 13), "D": (CASE_D, 14), "E": (CASE_E, 15), "F": (CASE_F, 16),
+         "G": (CASE_G, 17)}
 
 
 def make_folder(path: str, cfg: dict, seed: int) -> str:
@@ -113,10 +125,10 @@ def tokens_for(cfg: dict, n: int, seed: int) -> List[int]:
     return [rng.randrange(cfg["vocab"]) for _ in range(n)]
 
 
-# float32 engine against the float64 oracle: both sides' sums differ by float32 rounding; logits are O(1..10)
-F32_ATOL, F32_RTOL = 3e-5, 1e-4
+# float32 engine against the float64 oracle: the engine's sums are rounded to float32; logits are up to 1 in size
+F32_ATOL, F32_RTOL = 5e-6, 2e-5             # measured: up to 7e-7
 # bfloat16 engine: error relative to the root mean square of the reference logits of the sequence
-BF16_MAX_REL, BF16_MEAN_REL = 0.12, 0.02
+BF16_MAX_REL, BF16_MEAN_REL = 0.10, 0.015   # measured on the cases: 0.033 to 0.062 and 0.004 to 0.008
 
 
 def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -> None:

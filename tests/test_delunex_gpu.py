@@ -314,3 +314,22 @@ def test_command_line_and_trace_program(folders, tmp_path):
         got = replay_trace_run(folders[name], dtype, steps, str(tmp_path / dtype), max_tokens, cfg["vocab"])
         for rid, t in requests.items():
             assert_logits(got[rid], oracle(folders[name], t), dtype, f"trace_run/{dtype}/{rid}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "E"])
+def test_native_step_and_part_by_part_step_give_the_same_bits(folders, name, dtype):
+    """All layers of a step launched by one native call, or the parts called one by one from Python: the same kernels
+    with the same arguments, so the same bits, in prompt portions, mixed steps and recorded single-token steps."""
+    cfg = CASES[name][0]
+    requests = {f"n{i}": tokens_for(cfg, n, 80 + i) for i, n in enumerate([70, 9, 41])}
+    steps = trace_mixed(requests, 512, seed=2, max_live=3, tail=12)
+    out = []
+    for native in (True, False):
+        runner = runner_for(folders[name], dtype, max_tokens=512)
+        runner.model.native_step = native
+        out.append(replay_in_process(runner, steps))
+        # (a bfloat16 model whose first layer has no filter in front of its mixer is always run part by part)
+        assert (runner.model._native is not None) == (native and not (dtype == "bfloat16" and "canon" not in cfg))
+    for rid in requests:
+        assert torch.equal(out[0][rid], out[1][rid]), f"{name}/{dtype}/{rid}"
