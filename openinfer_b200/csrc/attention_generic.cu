@@ -1,4 +1,4 @@
-// Paged causal attention, general form: any head_dim that is a multiple of 8 (up to 256), any
+// Paged causal attention, general form: any head_dim that is a multiple of 8 (up to 512), any
 // number of heads and groups, an optional window, float32 or bfloat16 storage; prompt portions
 // and single decoded tokens alike. One warp per (token, query head).
 //
@@ -11,7 +11,7 @@
 // This is the kernel of the true 32-bit path and of every shape the tuned kernels refuse.
 #include "common.cuh"
 
-#define ATTN_MAX_HD 256
+#define ATTN_MAX_HD 512   // heads of more than 256 elements (a wide latent read as keys and values) get a second instance
 
 template <typename T>
 struct Vec16;  // 16 bytes of T
@@ -37,14 +37,14 @@ struct Vec16<bf16> {
   }
 };
 
-template <typename T, int kWarps>
+template <typename T, int kWarps, int kMaxHd>
 __global__ void attention_generic_kernel(
     const T* __restrict__ q, int q_row_stride, T* __restrict__ out, int out_row_stride,
     const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride, int page_size,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
     const int* __restrict__ positions, int nq, int nkv, int hd, float scale, int window, int tokens) {
   pdl_start();
-  __shared__ float q_sh[kWarps][ATTN_MAX_HD];
+  __shared__ float q_sh[kWarps][kMaxHd];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
   const int head = blockIdx.y * kWarps + warp;
@@ -62,7 +62,7 @@ __global__ void attention_generic_kernel(
   const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const size_t row_elems = (size_t)nkv * hd;
   constexpr int VN = Vec16<T>::N;
-  constexpr int kAccs = ATTN_MAX_HD / 32;
+  constexpr int kAccs = kMaxHd / 32;
   float acc[kAccs];
 #pragma unroll
   for (int r = 0; r < kAccs; ++r) acc[r] = 0.f;
@@ -126,19 +126,18 @@ OI_API int oi_attention_generic(const void* q, int q_row_stride, void* out, int 
   constexpr int kWarps = 4;
   dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
+#define OI_ATTN_GENERIC(T, MAXHD)                                                                                   \
+  oi_launch(attention_generic_kernel<T, kWarps, MAXHD>, grid, kWarps * 32, 0, s, (const T*)q, q_row_stride, (T*)out,  \
+            out_row_stride, (const T*)k_cache, (const T*)v_cache, page_stride, page_size, block_table, bt_stride,    \
+            token_req, positions, nq, nkv, hd, scale, window, tokens)
   if (dtype == OI_F32) {
-    oi_launch(attention_generic_kernel<float, kWarps>, grid, kWarps * 32, 0, s, 
-        (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache,
-        (const float*)v_cache, page_stride, page_size, block_table, bt_stride, token_req, positions, nq,
-        nkv, hd, scale, window, tokens);
+    if (hd <= 256) OI_ATTN_GENERIC(float, 256); else OI_ATTN_GENERIC(float, 512);
   } else if (dtype == OI_BF16) {
-    oi_launch(attention_generic_kernel<bf16, kWarps>, grid, kWarps * 32, 0, s, 
-        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache,
-        (const bf16*)v_cache, page_stride, page_size, block_table, bt_stride, token_req, positions, nq,
-        nkv, hd, scale, window, tokens);
+    if (hd <= 256) OI_ATTN_GENERIC(bf16, 256); else OI_ATTN_GENERIC(bf16, 512);
   } else {
     OI_REQUIRE(false, "attention: unknown dtype code %d", dtype);
   }
+#undef OI_ATTN_GENERIC
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

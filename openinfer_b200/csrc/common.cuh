@@ -132,6 +132,16 @@ __device__ __forceinline__ float gate_act(float g, int act) {
   return kFast ? __fdividef(g, 1.f + __expf(-t)) : g / (1.f + expf(-t));
 }
 
+// Activations of ONE argument, applied to a product's sums where they are complete (the codes continue the gate
+// activations'). OI_ACT_XIELU: a_p x^2 + x / 2 above zero, a_n (e^x - 1 - x) + x / 2 below, with the two numbers given.
+#define OI_ACT_XIELU 3
+template <bool kFast>
+__device__ __forceinline__ float unary_act(float x, int act, float p0, float p1) {
+  if (act != OI_ACT_XIELU) return x;
+  const float em1 = kFast ? __expf(x) - 1.f : expm1f(x);
+  return x > 0.f ? p0 * x * x + 0.5f * x : p1 * (em1 - x) + 0.5f * x;
+}
+
 template <typename T>
 __device__ __forceinline__ T from_f32(float x);
 template <>

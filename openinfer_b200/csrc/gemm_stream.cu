@@ -82,7 +82,9 @@ __device__ __forceinline__ float load_norm_weight(const OiStreamEpilogue& ep, in
 // kSiluMul: W's rows come in blocks of 64 gate rows followed by the 64 up rows of the same indices, so a
 // tile holds gate rows in lanes 0-63 of the accumulator and their up rows in lanes 64-127; the result
 // is out[M, N / 2] = act(gate) * up (act: OI_ACT_SILU or OI_ACT_GELU_TANH), formed where the K slices are added up.
-struct NoEpilogue {};
+struct NoEpilogue {
+  float p0, p1;   // the two numbers of an activation of one argument (act = OI_ACT_XIELU), else unused
+};
 
 // kEpi: 0 none; 1 the product follows a norm (rows scaled by the reciprocal root mean square); 2 it ends a residual branch
 template <int BN, typename TOut, bool kSiluMul, int kEpi>
@@ -93,6 +95,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   pdl_trigger();
   OiStreamEpilogue ep = {};
   if constexpr (kEpi != 0) ep = ep_arg;
+  float unary_p0 = 0.f, unary_p1 = 0.f;      // the numbers of an activation of one argument (act = OI_ACT_XIELU)
+  if constexpr (kEpi == 0) unary_p0 = ep_arg.p0, unary_p1 = ep_arg.p1;
   constexpr bool kFollowsNorm = kEpi == 1, kEndsBranch = kEpi == 2;   // the next kernel may be scheduled now: it reads nothing of ours before we are done
   using L = Layout<BN>;
   constexpr int kStages = L::kStages;
@@ -241,7 +245,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (n < N) {
 #pragma unroll
           for (int e = 0; e < 16; ++e)
-            if (c0 + e < M) out[(size_t)(c0 + e) * ldc + n] = from_f32<TOut>(__uint_as_float(v[e]));
+            if (c0 + e < M) out[(size_t)(c0 + e) * ldc + n] = from_f32<TOut>(unary_act<true>(__uint_as_float(v[e]), act, unary_p0, unary_p1));
         }
       } else {
         // Deposit this row's partial sums with the CTA that adds the row up. Rows are shared out evenly:
@@ -348,6 +352,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (live && (l & (chunk - 1)) == 0) sq_s[m * 4 + l / chunk] = sq;
         }
       } else {
+        if constexpr (!kSiluMul && kEpi == 0) {
+          sum = unary_act<true>(sum, act, unary_p0, unary_p1);
+        }
         if (valid) out[(size_t)m * ldc + col] = from_f32<TOut>(sum);
       }
     }
@@ -374,6 +381,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
+// an activation of one argument asked for by oi_gemm_stream_unary, for the launch that the same host thread makes next
+thread_local int g_unary_act = 0;
+thread_local float g_unary_p0 = 0.f, g_unary_p1 = 0.f;
+
 template <int BN, typename TOut, bool kSiluMul, int kEpi>
 int launch_variant(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N, int K,
                    int csize, int act, const OiStreamEpilogue& ep, cudaStream_t s) {
@@ -393,7 +404,7 @@ int launch_variant(void* out, long long ldc, const void* x, long long ldx, const
   const int kb_per_rank = (num_kb + csize - 1) / csize;
   if constexpr (kEpi == 0)
     oi_launch_cluster(kernel, dim3(csize, (N + BM - 1) / BM, 1), kThreads, L::kTotal, s, csize, mw, mx, (TOut*)out, ldc, M, N,
-                      num_kb, kb_per_rank, act, NoEpilogue{});
+                      num_kb, kb_per_rank, (!kSiluMul && g_unary_act) ? g_unary_act : act, NoEpilogue{g_unary_p0, g_unary_p1});
   else
     oi_launch_cluster(kernel, dim3(csize, (N + BM - 1) / BM, 1), kThreads, L::kTotal, s, csize, mw, mx, (TOut*)out, ldc, M, N,
                       num_kb, kb_per_rank, act, ep);
@@ -475,6 +486,17 @@ OI_API int oi_gemm_stream_fused(void* out, int out_dtype, long long ldc, const v
   else OI_STREAM(128);
 #undef OI_STREAM
   OI_REQUIRE(false, "gemm_stream: unknown output dtype code %d", out_dtype);
+}
+
+// The plain product with an activation of one argument applied to the sums where the K slices are added up:
+// out [M, N] = act(x W^T), act = OI_ACT_XIELU with its two numbers.
+OI_API int oi_gemm_stream_unary(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
+                                long long ldw, int M, int N, int K, int cluster_size, int act, float p0, float p1, void* stream) {
+  OI_REQUIRE(act == OI_ACT_XIELU, "gemm_stream_unary: unknown activation code %d", act);
+  g_unary_act = act, g_unary_p0 = p0, g_unary_p1 = p1;
+  const int rc = oi_gemm_stream_fused(out, out_dtype, ldc, x, ldx, W, ldw, M, N, K, cluster_size, OI_ACT_NONE, nullptr, stream);
+  g_unary_act = 0;
+  return rc;
 }
 
 // 0 when no bounded wait has run out since the last call; otherwise which role gave up (1 producer,

@@ -83,7 +83,7 @@ __device__ __forceinline__ void store_32(TOut* dst, const float (&a)[32], int va
 // `part` (0 or 1): which half of the tile's columns this warp takes.
 template <int BN, typename TOut, bool kSiluMul>
 __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __restrict__ C, long long ldc, int row, int n0,
-                                                  int M, int N, int act, int part) {
+                                                  int M, int N, int act, int part, float p0 = 0.f, float p1 = 0.f) {
   auto load = [&](int col, float (&a)[32]) {
     unsigned v[32];
     tmem_ld32(tmem_acc + (unsigned)col, v);
@@ -111,6 +111,10 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
     for (int c = part * (BN / kParts); c < (part + 1) * (BN / kParts); c += 32) {
       float a[32];
       load(c, a);
+      if (act != OI_ACT_NONE) {          // an activation of one argument on the finished sums
+#pragma unroll
+        for (int e = 0; e < 32; ++e) a[e] = unary_act<true>(a[e], act, p0, p1);
+      }
       if (row < M) store_32(C + (size_t)row * ldc + n0 + c, a, N - (n0 + c));
     }
   }
@@ -125,7 +129,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
 template <int BN, int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int act) {
+                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int act, float act_p0, float act_p1) {
   pdl_start();
   using L = Smem<BN, kStages>;
   extern __shared__ unsigned char smem_raw[];
@@ -227,7 +231,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part, act_p0, act_p1);
       // this warp has read its part of the accumulator: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -268,7 +272,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         TOut* __restrict__ C, long long ldc, int M, int N, int K, int act) {
+                         TOut* __restrict__ C, long long ldc, int M, int N, int K, int act, float act_p0, float act_p1) {
   pdl_start();
   constexpr int BN = 256, kPairM = 256;
   using L = Smem<128, kStages>;             // per CTA: 128 rows of A and 128 rows of W per stage
@@ -372,7 +376,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m0 = (tile % m_tiles) * kPairM + (int)rank * 128, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part, act_p0, act_p1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty_bar(a), 0));
@@ -398,7 +402,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // ------------------------------------------------------------------------------------------------
 template <int BN, int kStages, typename TOut, bool kSiluMul = false>
 int launch(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-           cudaStream_t s, int act = 0) {
+           cudaStream_t s, int act = 0, float p0 = 0.f, float p1 = 0.f) {
   CUtensorMap ma, mb;
   int rc = tc::make_map_2d_bf16(&ma, A, M, K, lda, BM);
   OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for A failed (%d; -1: cuTensorMapEncodeTiled is not available)", rc);
@@ -418,14 +422,14 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
     OI_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  oi_launch(kernel, tiles < sm_count ? tiles : sm_count, kThreads, smem, s, ma, mb, (TOut*)C, ldc, M, N, K, act);
+  oi_launch(kernel, tiles < sm_count ? tiles : sm_count, kThreads, smem, s, ma, mb, (TOut*)C, ldc, M, N, K, act, p0, p1);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
 
 template <int kStages, typename TOut, bool kSiluMul = false>
 int launch_pair(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-                cudaStream_t s, int act = 0) {
+                cudaStream_t s, int act = 0, float p0 = 0.f, float p1 = 0.f) {
   CUtensorMap ma, mb;
   int rc = tc::make_map_2d_bf16(&ma, A, M, K, lda, 128);
   OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for A failed (%d; -1: cuTensorMapEncodeTiled is not available)", rc);
@@ -446,7 +450,7 @@ int launch_pair(void* C, long long ldc, const void* A, long long lda, const void
   }
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  oi_launch_cluster(kernel, 2 * pairs, kThreads, smem, s, 2, ma, mb, (TOut*)C, ldc, M, N, K, act);
+  oi_launch_cluster(kernel, 2 * pairs, kThreads, smem, s, 2, ma, mb, (TOut*)C, ldc, M, N, K, act, p0, p1);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -500,6 +504,24 @@ OI_API int oi_gemm_tcgen05_pair(void* C, int c_dtype, long long ldc, const void*
   if (c_dtype == OI_BF16) return launch_pair<kPairStages, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
   if (c_dtype == OI_F32) return launch_pair<kPairStages, float>(C, ldc, A, lda, W, ldw, M, N, K, s);
   OI_REQUIRE(false, "gemm_tcgen05_pair: unknown output dtype code %d", c_dtype);
+}
+
+// The plain product with an activation of one argument (OI_ACT_XIELU with its two numbers) applied to the finished
+// sums in the epilogue: C [M, N] = act(A W^T). pair: 256 x 256 tiles by pairs of CTAs, else 128 x 256 by single CTAs.
+OI_API int oi_gemm_tcgen05_unary(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
+                                 long long ldw, int M, int N, int K, int pair, int act, float p0, float p1, void* stream) {
+  OI_REQUIRE(act == OI_ACT_XIELU, "gemm_tcgen05_unary: unknown activation code %d", act);
+  OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05_unary: bad sizes M=%d N=%d K=%d", M, N, K);
+  OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_unary: K and row strides must be multiples of 8");
+  OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05_unary: operands must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c_dtype == OI_BF16)
+    return pair ? launch_pair<kPairStages, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s, act, p0, p1)
+                : launch<256, 4, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s, act, p0, p1);
+  if (c_dtype == OI_F32)
+    return pair ? launch_pair<kPairStages, float>(C, ldc, A, lda, W, ldw, M, N, K, s, act, p0, p1)
+                : launch<256, 4, float>(C, ldc, A, lda, W, ldw, M, N, K, s, act, p0, p1);
+  OI_REQUIRE(false, "gemm_tcgen05_unary: unknown output dtype code %d", c_dtype);
 }
 
 // 0 when no bounded wait has run out since the last call; otherwise which role gave up

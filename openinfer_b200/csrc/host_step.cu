@@ -162,6 +162,26 @@ OI_API int oi_gated_mlp(void* out, const void* x, int dtype, int M, int hidden, 
   return oi_linear(out, dtype, hidden, act_buf, dtype, inter, w_down, w_down_dtype, inter, M, hidden, inter, stream);
 }
 
+OI_API int oi_dense_mlp(float* out, const void* x, int dtype, int M, int hidden, int inter, const void* w_up, int w_up_dtype,
+                        const void* w_down, int w_down_dtype, const void* act_pq, int pq_dtype, float a_p, float a_n, void* z_buf,
+                        void* stream) {
+  OI_REQUIRE(M >= 0 && hidden > 0 && inter > 0, "dense_mlp: bad sizes M=%d hidden=%d inter=%d", M, hidden, inter);
+  if (M == 0) return OI_OK;
+  // the activation in the up-projection's epilogue where a hand-written product takes the shape, else on its own
+  const bool fusable = dtype == OI_BF16 && w_up_dtype == OI_BF16 && tma_ok(x, hidden, w_up, hidden, hidden);
+  if (fusable && !g_opt[OI_OPT_BATCH_INVARIANT] && M <= kDecodeMaxRows && g_opt[OI_OPT_DECODE_GEMM] == 0) {
+    OI_TRY(oi_gemm_stream_unary(z_buf, dtype, inter, x, hidden, w_up, hidden, M, inter, hidden, stream_slices(inter, hidden),
+                                OI_ACT_XIELU, a_p, a_n, stream));
+  } else if (fusable && (M >= kFusedMinRows || g_opt[OI_OPT_BATCH_INVARIANT])) {   // 33..127 rows: the library's product is faster
+    const int pairs = !g_opt[OI_OPT_BATCH_INVARIANT] && M >= g_opt[OI_OPT_PAIR_MIN_ROWS] && (hidden > 2048 || M >= 2048);
+    OI_TRY(oi_gemm_tcgen05_unary(z_buf, dtype, inter, x, hidden, w_up, hidden, M, inter, hidden, pairs, OI_ACT_XIELU, a_p, a_n, stream));
+  } else {
+    OI_TRY(oi_linear(z_buf, dtype, inter, x, dtype, hidden, w_up, w_up_dtype, hidden, M, inter, hidden, stream));
+    OI_TRY(oi_xielu(z_buf, z_buf, dtype, act_pq, pq_dtype, (long long)M * inter, stream));
+  }
+  return oi_linear(out, OI_F32, hidden, z_buf, dtype, inter, w_down, w_down_dtype, inter, M, hidden, inter, stream);
+}
+
 OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* stream) {
   OI_REQUIRE(s && l, "attention_layer: null description");
   const int tokens = s->tokens;
@@ -392,9 +412,8 @@ OI_API int oi_forward_branch(const OiBranchModelDesc* m, const OiBranchStepDesc*
                               (!has_ff && averaged) ? st->hist : nullptr, hist_stride, results, L.depth_coef, L.depth_dtype,
                               st->low, stream));
     if (has_ff) {
-      OI_TRY(oi_linear(st->z, dt, L.inter, dt == OI_F32 ? (const void*)st->h : st->low, dt, H, L.w_up, L.w_up_dtype, H, T, L.inter, H, stream));
-      OI_TRY(oi_xielu(st->z, st->z, dt, L.act_pq, L.pq_dtype, (long long)T * L.inter, stream));
-      OI_TRY(oi_linear(st->branch, OI_F32, H, st->z, dt, L.inter, L.w_down, L.w_down_dtype, L.inter, T, H, L.inter, stream));
+      OI_TRY(oi_dense_mlp(st->branch, dt == OI_F32 ? (const void*)st->h : st->low, dt, T, H, L.inter, L.w_up, L.w_up_dtype, L.w_down,
+                          L.w_down_dtype, L.act_pq, L.pq_dtype, L.act_a_p, L.act_a_n, st->z, stream));
       OI_TRY(oi_branch_norm_add(st->h, st->branch, OI_F32, L.ff_norm_w, L.ff_norm_dtype, T, H, L.ff_eps, L.ff_offset,
                                 averaged ? st->hist : nullptr, hist_stride, results, L.depth_coef, L.depth_dtype, st->low, stream));
     }

@@ -111,6 +111,8 @@ OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x
        long ldw, int M, int N, int K, int cluster_size, int act, void* stream);
 OI_API int oi_gemm_stream_fused(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
        long long ldw, int M, int N, int K, int cluster_size, int act, const OiStreamEpilogue* epilogue, void* stream);
+OI_API int oi_gemm_stream_unary(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
+       long long ldw, int M, int N, int K, int cluster_size, int act, float p0, float p1, void* stream);
 OI_API int oi_gemm_stream_status(int* status);
 
 // gemm_tcgen05.cu
@@ -118,6 +120,8 @@ OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, l
        ldw, int M, int N, int K, int tile_n, int act, void* stream);
 OI_API int oi_gemm_tcgen05_pair(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W, long
        long ldw, int M, int N, int K, int act, void* stream);
+OI_API int oi_gemm_tcgen05_unary(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W, long
+       long ldw, int M, int N, int K, int pair, int act, float p0, float p1, void* stream);
 OI_API int oi_gemm_tcgen05_status(int* status);
 
 // rope_kv.cu
@@ -187,6 +191,13 @@ OI_API int oi_gated_mlp(void* out, const void* x, int dtype, int M, int hidden, 
        int w_gate_up_dtype, const void* w_down, int w_down_dtype, int act, int act_block, void* act_buf,
        void* gate_up_buf, void* stream);
 OI_API int oi_gated_mlp_needs_gate_up(int dtype, int w_dtype, int M, int hidden, int inter, int act_block);
+
+// down( act(up x) ) with one up-projection and the xIELU activation: out[M, hidden] in float32. `act_pq`: the
+// activation's two raw numbers on the device (read by the stand-alone activation kernel), a_p / a_n: the numbers the
+// formula uses, softplus(p) and 1/2 + softplus(q), formed by the host once (given to the products that apply the
+// activation in their epilogue: the weight stream up to 32 rows, the tcgen05 tiles beyond). `z_buf` [M, inter] in x's type.
+OI_API int oi_dense_mlp(float* out, const void* x, int dtype, int M, int hidden, int inter, const void* w_up, int w_up_dtype,
+       const void* w_down, int w_down_dtype, const void* act_pq, int pq_dtype, float a_p, float a_n, void* z_buf, void* stream);
 
 // What one step's attention calls share, per cache group and attention geometry: the step's metadata on the
 // device and the work items planned on the host.
@@ -300,14 +311,14 @@ typedef struct OiBranchLayerDesc {
   const void* ff_norm_w;      // [hidden] or null
   const void* w_up;           // [inter, hidden] or null (no feed-forward)
   const void* w_down;         // [hidden, inter]
-  const void* act_pq;         // the activation's two numbers
+  const void* act_pq;         // the activation's two numbers as stored; act_a_p / act_a_n: as the formula uses them
   const void* depth_coef;     // [depth_terms] or null
   long long conv_state_stride;
   int conv_w_dtype, taps, add_input;
   int w_in_dtype, w_out_dtype, latent_norm_dtype, mixer_norm_dtype, ff_norm_dtype, w_up_dtype, w_down_dtype, pq_dtype, depth_dtype;
   int in_cols, heads, row, rank, window, latent_off, gate_off, has_gate;
   int attn_step, inter, depth_terms;
-  float scale, latent_eps, latent_offset, mixer_eps, mixer_offset, ff_eps, ff_offset;
+  float scale, latent_eps, latent_offset, mixer_eps, mixer_offset, ff_eps, ff_offset, act_a_p, act_a_n;
 } OiBranchLayerDesc;
 
 typedef struct OiBranchModelDesc {

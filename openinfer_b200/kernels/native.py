@@ -102,7 +102,7 @@ class BranchLayerDesc(Structure):
         ("gate_off", c_int), ("has_gate", c_int),
         ("attn_step", c_int), ("inter", c_int), ("depth_terms", c_int),
         ("scale", c_float), ("latent_eps", c_float), ("latent_offset", c_float), ("mixer_eps", c_float), ("mixer_offset", c_float),
-        ("ff_eps", c_float), ("ff_offset", c_float),
+        ("ff_eps", c_float), ("ff_offset", c_float), ("act_a_p", c_float), ("act_a_n", c_float),
     ]
 
 
@@ -140,6 +140,7 @@ def declare(lib) -> None:
     lib.oi_gated_mlp_needs_gate_up.argtypes, lib.oi_gated_mlp_needs_gate_up.restype = [I, I, I, I, I, I], c_int
     lib.oi_attention_layer.argtypes, lib.oi_attention_layer.restype = [POINTER(AttnStep), POINTER(AttnLayer), P], c_int
     lib.oi_forward.argtypes, lib.oi_forward.restype = [POINTER(ModelDesc), POINTER(StepDesc), P], c_int
+    lib.oi_dense_mlp.argtypes, lib.oi_dense_mlp.restype = [P, P, I, I, I, I, P, I, P, I, P, I, c_float, c_float, P, P], c_int
     lib.oi_forward_branch.argtypes, lib.oi_forward_branch.restype = [POINTER(BranchModelDesc), POINTER(BranchStepDesc), P], c_int
     lib.oi_launches.argtypes, lib.oi_launches.restype = [], ctypes.c_ulonglong
     lib.oi_launch_fence.argtypes, lib.oi_launch_fence.restype = [], c_int

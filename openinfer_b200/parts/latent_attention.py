@@ -48,8 +48,8 @@ class LatentAttention(Mixer):
         if s.window is not None and s.window <= 0:
             raise ValueError(f"latent_attention: window must be positive, got {s.window}")
         self.row = _round_up(s.latent_rank, 8)          # elements of a cached row
-        if self.row > 256:
-            raise ValueError(f"latent_attention: latent_rank {s.latent_rank} is beyond what the attention kernels take (256)")
+        if self.row > 512:
+            raise ValueError(f"latent_attention: latent_rank {s.latent_rank} is beyond what the attention kernels take (512)")
         self.q_cols = s.num_heads * (self.row if s.absorb == "weights" else s.qk_dim)
         self.latent_off = self.q_cols
         self.gate_off = self.latent_off + (s.latent_rank if s.has_latent else 0)

@@ -102,9 +102,26 @@ class DenseMlp(FeedForward):
         self.w_up = tensors[s.up_name].contiguous()
         self.w_down = tensors[s.down_name].contiguous()
         self.act = tensors[s.act_name].contiguous()
+        # the numbers the formula uses, for the products that apply the activation in their epilogue (float32, as the
+        # stand-alone kernel forms them on the device)
+        pq = self.act.detach().to(torch.float32).cpu()
+        soft = torch.nn.functional.softplus(pq)
+        self.a_p, self.a_n = float(soft[0]), float(0.5 + soft[1])
 
     def forward(self, x: torch.Tensor, ctx, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        from ..kernels.linear import linear
-        z = linear(x, self.w_up)
-        ops.xielu(z, z, self.act)
-        return linear(z, self.w_down, out_dtype=out_dtype)
+        """One native call (``oi_dense_mlp``): the up-projection with the activation in its epilogue where a hand-written
+        product takes the shape (else the plain product and the activation kernel), then the down-projection, float32."""
+        s = self.spec
+        M = x.shape[0]
+        if not x.is_contiguous():
+            x = x.contiguous()
+        if M > 32:
+            ensure_library(x.device)
+        codes = native.DTYPE_CODE
+        out = torch.empty((M, s.hidden_size), dtype=torch.float32, device=x.device)
+        z = torch.empty((M, s.intermediate_size), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.load().oi_dense_mlp(out.data_ptr(), x.data_ptr(), codes[x.dtype], M, s.hidden_size, s.intermediate_size,
+                                            self.w_up.data_ptr(), codes[self.w_up.dtype], self.w_down.data_ptr(),
+                                            codes[self.w_down.dtype], self.act.data_ptr(), codes[self.act.dtype], self.a_p,
+                                            self.a_n, z.data_ptr(), _lib.current_stream()), "dense_mlp")
+        return out if out_dtype in (None, torch.float32) else out.to(out_dtype)

@@ -299,6 +299,7 @@ class Model:
                 L.ff_norm_w, L.ff_norm_dtype, L.ff_eps, L.ff_offset = fn.weight.data_ptr(), codes[fn.weight.dtype], fn.spec.eps, fn.spec.weight_offset
                 L.w_up, L.w_up_dtype, L.w_down, L.w_down_dtype = ff.w_up.data_ptr(), codes[ff.w_up.dtype], ff.w_down.data_ptr(), codes[ff.w_down.dtype]
                 L.act_pq, L.pq_dtype, L.inter = ff.act.data_ptr(), codes[ff.act.dtype], ff.spec.intermediate_size
+                L.act_a_p, L.act_a_n = ff.a_p, ff.a_n
             if b.depth is not None:
                 L.depth_coef, L.depth_dtype, L.depth_terms = b.depth.weight.data_ptr(), codes[b.depth.weight.dtype], b.depth.weight.numel()
         sp = self.spec

@@ -83,8 +83,14 @@ CASE_G = {
     "norm": {"eps": 1e-6}, "canon": {"taps": 2},
     "layers": [_layer(7, 5, 3, 9, 1.0, window=5, ff=21), _layer(1, 2, 2, 9, 1.0, kv_from=0)],
 }
+# a latent wider than 256 numbers (the general attention kernel's second instance)
+CASE_H = {
+    "architecture": "Delunex", "vocab": 64, "width": 56, "logit_scale": 1.0, "embedding": {"scale": 4.0},
+    "norm": {"eps": 1e-6}, "canon": {"taps": 3},
+    "layers": [_layer(2, 8, 8, 320, 1.2, window=30, ff=32), _layer(3, 8, 8, 320, 0.9, window=12, kv_from=0)],
+}
 CASES = {"A": (CASE_A, 11), "B": (CASE_B, 12), "C": (CASE_C, 13), "D": (CASE_D, 14), "E": (CASE_E, 15), "F": (CASE_F, 16),
-         "G": (CASE_G, 17)}
+         "G": (CASE_G, 17), "H": (CASE_H, 18)}
 
 
 def make_folder(path: str, cfg: dict, seed: int) -> str:

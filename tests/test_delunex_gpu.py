@@ -333,3 +333,27 @@ def test_native_step_and_part_by_part_step_give_the_same_bits(folders, name, dty
         assert (runner.model._native is not None) == (native and not (dtype == "bfloat16" and "canon" not in cfg))
     for rid in requests:
         assert torch.equal(out[0][rid], out[1][rid]), f"{name}/{dtype}/{rid}"
+
+
+@pytest.mark.parametrize("rows", [1, 8, 32, 33, 100, 300, 2100])
+def test_dense_feed_forward_with_the_activation_in_the_products_epilogue(rows):
+    """bfloat16 at sizes the tensor-core products take: up to 32 rows the weight stream applies the activation where it
+    adds up its K slices, beyond that the tcgen05 tiles in their epilogue (pairs of CTAs from 2,048 rows); the result is
+    the plain feed-forward's. A size they refuse goes through the plain product and the activation kernel."""
+    from openinfer_b200.parts.mlp import DenseMlp
+    from openinfer_b200.parts.spec import DenseMlpSpec
+    from openinfer_b200.kernels import gemm_tcgen05, linear
+    g = torch.Generator().manual_seed(rows)
+    for hidden, inter in ((256, 768), (72, 100)):
+        part = DenseMlp(DenseMlpSpec(hidden_size=hidden, intermediate_size=inter))
+        w = {"up": torch.randn(inter, hidden, generator=g) * hidden ** -0.5, "down": torch.randn(hidden, inter, generator=g) * inter ** -0.5,
+             "act": torch.tensor([0.4, -0.8])}
+        w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+        part.load({k: _dev(v) for k, v in w.items()})
+        x = (torch.randn(rows, hidden, generator=g) * 1.5).to(torch.bfloat16)
+        got = part.forward(_dev(x), None)
+        assert got.dtype == torch.float32
+        ref = plain.dense_ff(x.double(), w["up"].double(), w["down"].double(), w["act"].double())
+        err = (got.double().cpu() - ref).abs().max().item() / ref.abs().max().item()
+        assert err < 2e-2, f"rows {rows} hidden {hidden}: {err}"
+    assert gemm_tcgen05.status() == 0 and linear.stream_status() == 0
