@@ -57,6 +57,10 @@ class StateNeed:
 
     shape: Tuple[int, ...]
     dtype: str = "float32"  # "float32" or "model" (the model's activation dtype)
+    # 2: the tensor holds two copies per slot, [slots, 2, *shape]; a step reads copy `state_phase(request)` and writes the
+    # other one, so that ONE kernel can read a request's old state in some of its rows while it writes the new state in
+    # others. The phase turns over when a step of the request is committed.
+    phases: int = 1
 
 
 @dataclasses.dataclass(frozen=True)
@@ -93,6 +97,7 @@ class _Request:
     reserved: int = 0                # tokens reserved beyond num_tokens by the step in flight
     new_pages: Optional[List[List[int]]] = None  # pages taken by that reservation, per group
     state_slot: int = -1
+    steps: int = 0                   # committed steps: its parity says which copy of a two-phase state is current
     # prefix cache: the registered blocks behind table entries [0, len(blocks)); the lineage key after
     # them; tokens known beyond them; whether further pages may still be registered
     blocks: List[_Block] = dataclasses.field(default_factory=list)
@@ -174,7 +179,8 @@ class CacheManager:
                     dtype=dtype, device=device)
             for need in self.state_needs:
                 sdtype = dtype if need.dtype == "model" else torch.float32
-                self.state_tensors.append(torch.zeros((max_requests, *need.shape), dtype=sdtype, device=device))
+                shape = (max_requests, need.phases, *need.shape) if need.phases > 1 else (max_requests, *need.shape)
+                self.state_tensors.append(torch.zeros(shape, dtype=sdtype, device=device))
         self._allocated = True
 
     # ------------------------------------------------------------------
@@ -303,6 +309,10 @@ class CacheManager:
     def state_slot(self, request_id: Hashable) -> int:
         return self.requests[request_id].state_slot
 
+    def state_phase(self, request_id: Hashable) -> int:
+        """Which copy of a two-phase state the request's next step reads (it writes the other)."""
+        return self.requests[request_id].steps & 1
+
     def reserve(self, request_id: Hashable, new_tokens: int) -> int:
         """Take the pages for positions [n, n + new_tokens) in every group; returns n.
 
@@ -348,6 +358,7 @@ class CacheManager:
         if not r.reserved:
             raise RuntimeError(f"request {request_id!r} has no reservation to commit")
         count = r.reserved
+        r.steps += 1
         r.num_tokens += r.reserved
         r.reserved = 0
         r.new_pages = None

@@ -90,20 +90,24 @@ __global__ void history_average_kernel(float* __restrict__ h, float* __restrict_
 
 // ---------------------------------------------------------------------------------------------
 // out[t, c] = x[t, c] + sum_{j < taps} w[c, j] * x_(t - taps + 1 + j)[c]: inputs before the portion's first row come
-// from the request's state (the last taps - 1 inputs of earlier steps, zeros before the sequence's start).
+// from the request's state (the last taps - 1 inputs of earlier steps, zeros before the sequence's start). The state
+// holds two copies per request, [slots][2][taps - 1][channels]: a step reads copy state_phase[request] and leaves the
+// state as it stands after the step in the other copy (the host turns the phase over when the step is committed), so
+// that rows which read the old state and rows which write the new one can run in one kernel.
 // ---------------------------------------------------------------------------------------------
 template <typename TX, typename TO>
 __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype,
                                   const float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ token_req, const int* __restrict__ state_slots, int channels,
-                                  int taps, int add_input) {
+                                  const int* __restrict__ token_req, const int* __restrict__ state_slots,
+                                  const int* __restrict__ state_phase, int channels, int taps, int add_input) {
   pdl_start();
   const int t = blockIdx.x;
   const int req = token_req[t];
   const int start = req >= 0 ? cu_seqlens[req] : t;
   const int rel = t - start;
-  const float* st = req >= 0 ? state + (size_t)state_slots[req] * state_stride : nullptr;
   const int keep = taps - 1;
+  const float* st = (req >= 0 && keep > 0) ? state + (size_t)state_slots[req] * state_stride + (size_t)state_phase[req] * keep * channels
+                                           : nullptr;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     const float cur = to_f32(x[(size_t)t * channels + c]);
     float acc = add_input ? cur : 0.f;
@@ -120,20 +124,23 @@ __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x
   }
 }
 
-// state <- the last taps - 1 inputs of (state, this step's rows), per request and channel
+// the other copy of the state <- the last taps - 1 inputs of (current copy, this step's rows), per request and channel
 template <typename TX>
 __global__ void short_conv_state_kernel(float* __restrict__ state, long long state_stride, const TX* __restrict__ x,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
-                                        const int* __restrict__ state_slots, int channels, int keep) {
+                                        const int* __restrict__ state_slots, const int* __restrict__ state_phase, int channels,
+                                        int keep) {
   pdl_start();
   const int b = blockIdx.x;
   const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
   if (n <= 0 || token_req[start] < 0) return;   // a padding request of a recorded step owns no state
-  float* st = state + (size_t)state_slots[b] * state_stride;
+  const int phase = state_phase[b];
+  const float* old = state + (size_t)state_slots[b] * state_stride + (size_t)phase * keep * channels;
+  float* st = state + (size_t)state_slots[b] * state_stride + (size_t)(1 - phase) * keep * channels;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-    for (int k = 0; k < keep; ++k) {   // ascending: entry k takes what lies n places further on, or a row of the step
+    for (int k = 0; k < keep; ++k) {
       const int s = n + k - keep;
-      st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * channels + c]) : st[(size_t)(k + n) * channels + c];
+      st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * channels + c]) : old[(size_t)(k + n) * channels + c];
     }
   }
 }
@@ -286,10 +293,10 @@ __global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const TA* __re
 constexpr int kConvRows = 4;
 constexpr int kConvMaxTaps = 8;
 template <typename TX, typename TO, int kTaps>     // kTaps: 2, 4 or 8, at least the taps
-__global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype,
-                                      const float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
-                                      const int* __restrict__ token_req, const int* __restrict__ state_slots, int tokens,
-                                      int channels, int taps, int add_input) {
+__global__ void __launch_bounds__(256) short_conv_vec_kernel(
+    TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype, float* __restrict__ state,
+    long long state_stride, const int* __restrict__ token_req, const int* __restrict__ state_slots,
+    const int* __restrict__ state_phase, int tokens, int channels, int taps, int add_input, int update_state) {
   pdl_trigger();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   const int t0 = blockIdx.x * kConvRows;
@@ -305,7 +312,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ ou
   }
   pdl_wait();
   if (c >= channels) return;
-  // ring[(row - 1 - i) mod taps]: the input i + 1 rows above the current one
+  // ring[i]: the input i + 1 rows above the current one
   float ring[kTaps][4];
 #pragma unroll
   for (int j = 0; j < kTaps; ++j) {
@@ -313,14 +320,16 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ ou
     if (j < keep && r >= 0) load4(x + (size_t)r * channels + c, ring[j]);
   }
   const int t_end = min(tokens, t0 + kConvRows);
-  // the requests of the rows and of the taps - 1 rows above them, and the rows' inputs: all asked for before any is used.
-  // A request's rows are consecutive, so a row's place in its portion shows in its neighbours' requests alone.
-  int reqs[kConvRows + kTaps - 1];
+  // The requests of the rows, of the taps - 1 rows above and of the taps - 1 rows below them, and the rows' inputs: all
+  // asked for before any is used. A request's rows are consecutive, so a row's place in its portion (from the front
+  // and from the end) shows in its neighbours' requests alone.
+  constexpr int kSpan = kConvRows + 2 * (kTaps - 1);
+  int reqs[kSpan];
   float curs[kConvRows][4];
 #pragma unroll
-  for (int i = 0; i < kConvRows + kTaps - 1; ++i) {
+  for (int i = 0; i < kSpan; ++i) {
     const int r = t0 - (kTaps - 1) + i;
-    reqs[i] = (r >= 0 && r < t_end && r >= t0 - keep) ? token_req[r] : -2;
+    reqs[i] = (r >= 0 && r < tokens && r >= t0 - keep && r < t_end + keep) ? token_req[r] : -2;
   }
 #pragma unroll
   for (int i = 0; i < kConvRows; ++i)
@@ -330,11 +339,18 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ ou
     const int t = t0 + i;
     if (t >= t_end) break;
     const int req = reqs[i + kTaps - 1];
-    int rel = 0;                 // rows of the same request directly above, up to taps - 1
+    int rel = 0, after = 0;      // rows of the same request directly above / below, counted up to taps - 1
 #pragma unroll
-    for (int j = 1; j < kTaps; ++j)
+    for (int j = 1; j < kTaps; ++j) {
       if (j <= keep && rel == j - 1 && reqs[i + kTaps - 1 - j] == req) rel = j;
-    const float* st = (req >= 0 && rel < keep) ? state + (size_t)state_slots[req] * state_stride : nullptr;
+      if (j <= keep && after == j - 1 && reqs[i + kTaps - 1 + j] == req) after = j;
+    }
+    // the request's state: the copy this step reads, and the one it leaves behind
+    const bool touches = req >= 0 && keep > 0 && (rel < keep || (update_state && after < keep));
+    float* base = touches ? state + (size_t)state_slots[req] * state_stride : nullptr;
+    const int phase = touches ? state_phase[req] : 0;
+    const float* st = base ? base + (size_t)phase * keep * channels : nullptr;
+    float* nx = (base && update_state) ? base + (size_t)(1 - phase) * keep * channels : nullptr;
     float cur[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) cur[e] = curs[i][e];
@@ -342,7 +358,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ ou
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[e] = add_input ? cur[e] : 0.f;
 #pragma unroll
-    for (int j = 0; j < kTaps; ++j) {     // tap keep - j reads the input j rows above (j = 0: the row itself)
+    for (int j = 0; j < kTaps; ++j) {     // j = 0: the row itself; j > 0: the input j rows above
       if (j >= taps) break;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (j == 0) {
@@ -358,6 +374,19 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(TO* __restrict__ ou
       for (int e = 0; e < 4; ++e) acc[e] += wt[j][e] * v[e];
     }
     store4(out + (size_t)t * channels + c, acc);
+    if (nx != nullptr && after < keep) {
+      // one of the portion's last taps - 1 rows: its input is entry keep - 1 - after of the state left behind
+      store4(nx + (size_t)(keep - 1 - after) * channels + c, cur);
+      if (rel == 0 && after + 1 < keep) {
+        // the portion's first row, and the portion (after + 1 rows) is shorter than the state: the old entries move up
+        const int n = after + 1;
+        for (int k = 0; k < keep - n; ++k) {
+          float v[4];
+          load4(st + (size_t)(k + n) * channels + c, v);
+          store4(nx + (size_t)k * channels + c, v);
+        }
+      }
+    }
 #pragma unroll
     for (int j = kTaps - 1; j > 0; --j) {
 #pragma unroll
@@ -487,12 +516,13 @@ OI_API int oi_history_average(float* h, float* hist, long long hist_stride, int 
 }
 
 OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float* state,
-                         long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots, int tokens,
-                         int requests, int channels, int taps, int add_input, int update_state, void* stream) {
+                         long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots,
+                         const int* state_phase, int tokens, int requests, int channels, int taps, int add_input, int update_state,
+                         void* stream) {
   OI_REQUIRE(tokens >= 0 && requests >= 0 && channels > 0 && taps >= 1, "short_conv: bad sizes tokens=%d channels=%d taps=%d",
              tokens, channels, taps);
-  OI_REQUIRE(taps == 1 || (state != nullptr && state_stride >= (long long)(taps - 1) * channels),
-             "short_conv: %d taps need a state of %d rows per request", taps, taps - 1);
+  OI_REQUIRE(taps == 1 || (state != nullptr && state_phase != nullptr && state_stride >= 2LL * (taps - 1) * channels),
+             "short_conv: %d taps need a state of two copies of %d rows per request, and the requests' phases", taps, taps - 1);
   if (tokens == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int cy = (channels + kRowThreads - 1) / kRowThreads;
@@ -501,24 +531,24 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
                    (taps == 1 || (aligned16(state) && state_stride % 4 == 0));
   const int vthreads = channels / 4 >= 256 ? 256 : ((channels / 4 + 31) / 32) * 32;
   const dim3 vgrid((tokens + kConvRows - 1) / kConvRows, vec ? (channels / 4 + vthreads - 1) / vthreads : 1);
+#define OI_CONV_VEC(TX, TO, KT)                                                                                          \
+  oi_launch(short_conv_vec_kernel<TX, TO, KT>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, state, state_stride, \
+            token_req, state_slots, state_phase, tokens, channels, taps, add_input, update_state)
 #define OI_CONV_CASE(XD, OD, TX, TO)                                                                                     \
   if (x_dtype == XD && out_dtype == OD) {                                                                                \
-    if (vec && taps <= 2)                                                                                                \
-      oi_launch(short_conv_vec_kernel<TX, TO, 2>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
-                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
-    else if (vec && taps <= 4)                                                                                           \
-      oi_launch(short_conv_vec_kernel<TX, TO, 4>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
-                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
-    else if (vec)                                                                                                        \
-      oi_launch(short_conv_vec_kernel<TX, TO, 8>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype,             \
-                (const float*)state, state_stride, cu_seqlens, token_req, state_slots, tokens, channels, taps, add_input); \
-    else                                                                                                                 \
+    if (vec) {                                                                                                           \
+      if (taps <= 2) OI_CONV_VEC(TX, TO, 2);                                                                             \
+      else if (taps <= 4) OI_CONV_VEC(TX, TO, 4);                                                                        \
+      else OI_CONV_VEC(TX, TO, 8);                                                                                       \
+      OI_CHECK_LAUNCH();                                                                                                 \
+      return OI_OK;                                                                                                      \
+    }                                                                                                                    \
     oi_launch(short_conv_kernel<TX, TO>, grid, kRowThreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, (const float*)state, \
-              state_stride, cu_seqlens, token_req, state_slots, channels, taps, add_input);                              \
+              state_stride, cu_seqlens, token_req, state_slots, state_phase, channels, taps, add_input);                 \
     OI_CHECK_LAUNCH();                                                                                                   \
     if (update_state && taps > 1) {                                                                                      \
       oi_launch(short_conv_state_kernel<TX>, dim3(requests, cy), kRowThreads, 0, s, state, state_stride, (const TX*)x,    \
-                cu_seqlens, token_req, state_slots, channels, taps - 1);                                                 \
+                cu_seqlens, token_req, state_slots, state_phase, channels, taps - 1);                                    \
       OI_CHECK_LAUNCH();                                                                                                 \
     }                                                                                                                    \
     return OI_OK;                                                                                                        \
@@ -527,6 +557,7 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
   OI_CONV_CASE(OI_F32, OI_BF16, float, bf16)
   OI_CONV_CASE(OI_BF16, OI_BF16, bf16, bf16)
 #undef OI_CONV_CASE
+#undef OI_CONV_VEC
   OI_REQUIRE(false, "short_conv: dtype codes %d -> %d are not supported", x_dtype, out_dtype);
 }
 

@@ -379,7 +379,7 @@ OI_API int oi_forward_branch(const OiBranchModelDesc* m, const OiBranchStepDesc*
     const void* u = st->u;
     if (L.conv_w) {
       OI_TRY(oi_short_conv(st->u, dt, st->h, OI_F32, L.conv_w, L.conv_w_dtype, L.conv_state, L.conv_state_stride, st->cu_seqlens,
-                           st->token_req, st->state_slots, T, st->requests, H, L.taps, L.add_input, 1, stream));
+                           st->token_req, st->state_slots, st->state_phase, T, st->requests, H, L.taps, L.add_input, 1, stream));
     } else if (dt == OI_F32) {
       u = st->h;
     } else {

@@ -76,8 +76,8 @@ OI_API int oi_branch_norm_add(float* h, const void* a, int a_dtype, const void* 
 OI_API int oi_history_average(float* h, float* hist, long long hist_stride, int n_prev, const void* coef, int
        coef_dtype, long long n, void* stream);
 OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float*
-       state, long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots, int tokens,
-       int requests, int channels, int taps, int add_input, int update_state, void* stream);
+       state, long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots, const int*
+       state_phase, int tokens, int requests, int channels, int taps, int add_input, int update_state, void* stream);
 OI_API int oi_latent_store(void* pages, long long page_stride, int page_size, int row_elems, const void* src, long
        long src_stride, int dtype, const void* w, int w_dtype, const int* slots, int tokens, int rank, float eps,
        float w_offset, void* stream);
@@ -302,7 +302,7 @@ OI_API int oi_forward(const OiModelDesc* model, const OiStepDesc* step, void* st
 // ------------------------------------------------------------------------------------------------
 typedef struct OiBranchLayerDesc {
   const void* conv_w;         // [hidden, taps] or null: the mixer then reads the stream as it is
-  float* conv_state;          // [slots, taps - 1, hidden] or null (one tap)
+  float* conv_state;          // [slots, 2, taps - 1, hidden] or null (one tap)
   const void* w_in;           // [in_cols, hidden]: queries | latent | gate | zero rows
   const void* w_out;          // [hidden, heads * row]
   const void* latent_norm_w;  // [rank] or null (the layer reads another layer's latent)
@@ -338,6 +338,7 @@ typedef struct OiBranchStepDesc {
   const int* cu_seqlens;
   const int* token_req;
   const int* state_slots;
+  const int* state_phase;     // [requests] which copy of a two-phase state the step reads
   float* h;                   // [tokens, hidden] the stream
   float* hist;                // [num_layers + 1, tokens, hidden] or null (no layer averages)
   void* u;                    // [tokens, hidden] what the mixer reads, in the model's type

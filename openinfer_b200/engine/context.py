@@ -41,6 +41,7 @@ class StepContext:
     starts_host: List[int] = dataclasses.field(default_factory=list)   # position of each request's first row
     kv_lens_host: List[int] = dataclasses.field(default_factory=list)
     state_slots_host: List[int] = dataclasses.field(default_factory=list)
+    state_phase: Any = None      # int32 [requests]: which copy of a two-phase state this step reads (device tensor)
     decode_only: bool = False    # every request brings exactly one row
     max_q_len: int = 0
     max_kv_len: int = 0

@@ -260,7 +260,7 @@ class ModelRunner:
         sections: Dict[str, int] = {}
         off = 0
         for name, size in (("token_ids", T), ("token_src", T), ("positions", T), ("token_req", T), ("cu_seqlens", B + 1),
-                           ("state_slots", B)):
+                           ("state_slots", B), ("state_phase", B)):
             sections[name] = off
             off += _align4(size)
         for g in range(G):
@@ -287,6 +287,8 @@ class ModelRunner:
         src = view("token_src", T)
         cu = view("cu_seqlens", B + 1)
         slots_host = view("state_slots", B)
+        phase_host = view("state_phase", B)
+        phase_host[:] = 0
         tok[:] = 0
         src[:] = -1
         pos[:] = 0
@@ -303,6 +305,7 @@ class ModelRunner:
                 src[row] = e.token_from
             cu[b] = row
             slots_host[b] = cache.state_slot(e.request_id)
+            phase_host[b] = cache.state_phase(e.request_id)
             want_rows.extend(row + int(w) for w in e.want)
             row += n
         for b in range(len(entries), B + 1):   # padding requests bring one row each
@@ -342,7 +345,7 @@ class ModelRunner:
         return StepContext(
             num_tokens=T, num_requests=B, token_ids=dview("token_ids", T), positions=dview("positions", T),
             token_req=dview("token_req", T), cu_seqlens=dview("cu_seqlens", B + 1),
-            state_slots=dview("state_slots", B), groups=groups, cache=cache,
+            state_slots=dview("state_slots", B), state_phase=dview("state_phase", B), groups=groups, cache=cache,
             q_lens_host=q_lens, starts_host=list(starts), kv_lens_host=kv_lens, state_slots_host=slots,
             decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens), max_kv_len=max(kv_lens))
 

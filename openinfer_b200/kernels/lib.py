@@ -54,7 +54,7 @@ _SIGNATURES = {
     "oi_rmsnorm_cast": [P, I, P, I, P, I, P, I, I, F, F, P],
     "oi_branch_norm_add": [P, P, I, P, I, I, I, F, F, P, L, I, P, I, P, P],
     "oi_history_average": [P, P, L, I, P, I, L, P],
-    "oi_short_conv": [P, I, P, I, P, I, P, L, P, P, P, I, I, I, I, I, I, P],
+    "oi_short_conv": [P, I, P, I, P, I, P, L, P, P, P, P, I, I, I, I, I, I, P],
     "oi_latent_store": [P, L, I, I, P, L, I, P, I, P, I, I, F, F, P],
     "oi_head_gate": [P, L, P, L, I, I, I, I, P],
     "oi_xielu": [P, P, I, P, I, L, P],

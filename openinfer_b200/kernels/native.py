@@ -119,7 +119,7 @@ class BranchModelDesc(Structure):
 class BranchStepDesc(Structure):
     _fields_ = [
         ("token_ids", c_void_p), ("attn_steps", POINTER(AttnStep)), ("want_rows", c_void_p), ("cu_seqlens", c_void_p),
-        ("token_req", c_void_p), ("state_slots", c_void_p),
+        ("token_req", c_void_p), ("state_slots", c_void_p), ("state_phase", c_void_p),
         ("h", c_void_p), ("hist", c_void_p), ("u", c_void_p), ("low", c_void_p), ("proj", c_void_p), ("mixed", c_void_p),
         ("branch", c_void_p), ("z", c_void_p), ("wanted", c_void_p), ("logits", c_void_p),
         ("tokens", c_int), ("requests", c_int), ("num_attn_steps", c_int), ("num_want", c_int),

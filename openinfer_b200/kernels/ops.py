@@ -404,14 +404,15 @@ def history_average(h: torch.Tensor, history: torch.Tensor, n_prev: int, coef: t
 
 
 def short_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor],
-               cu_seqlens: torch.Tensor, token_req: torch.Tensor, state_slots: torch.Tensor, *, add_input: bool = True,
-               update_state: bool = True) -> torch.Tensor:
+               cu_seqlens: torch.Tensor, token_req: torch.Tensor, state_slots: torch.Tensor,
+               state_phase: Optional[torch.Tensor] = None, *, add_input: bool = True, update_state: bool = True) -> torch.Tensor:
     """Causal convolution over time on each channel, per request of a flattened step:
-    out[t] = (x[t] if add_input) + sum_j weight[:, j] * x_(t - taps + 1 + j). ``state`` float32 [slots, taps - 1,
-    channels] holds every request's last taps - 1 inputs (zeros before its start); with ``update_state`` it is
-    moved on by this step's rows afterwards. x float32 or the type of out."""
-    _cuda(out, x, weight, state, cu_seqlens, token_req, state_slots)
-    for t, what in ((cu_seqlens, "cu_seqlens"), (token_req, "token_req"), (state_slots, "state_slots")):
+    out[t] = (x[t] if add_input) + sum_j weight[:, j] * x_(t - taps + 1 + j). ``state`` float32 [slots, 2, taps - 1,
+    channels] holds every request's last taps - 1 inputs (zeros before its start) in two copies: the step reads copy
+    ``state_phase[request]`` and, with ``update_state``, leaves the state moved on by its rows in the other copy (the
+    caller turns the phase over afterwards). x float32 or the type of out."""
+    _cuda(out, x, weight, state, cu_seqlens, token_req, state_slots, state_phase)
+    for t, what in ((cu_seqlens, "cu_seqlens"), (token_req, "token_req"), (state_slots, "state_slots"), (state_phase, "state_phase")):
         _i32(t, f"short_conv {what}")
     tokens, channels = x.shape
     taps = weight.shape[1]
@@ -419,13 +420,16 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, state: 
         raise KernelError(f"short_conv: shapes x={tuple(x.shape)} out={tuple(out.shape)} weight={tuple(weight.shape)}")
     stride = 0
     if taps > 1:
-        if state is None or state.dtype != torch.float32 or state.shape[1:] != (taps - 1, channels) or not state.is_contiguous():
-            raise KernelError(f"short_conv: {taps} taps need a contiguous float32 state [slots, {taps - 1}, {channels}]")
+        if (state is None or state.dtype != torch.float32 or state.shape[1:] != (2, taps - 1, channels) or not state.is_contiguous()
+                or state_phase is None):
+            raise KernelError(f"short_conv: {taps} taps need a contiguous float32 state [slots, 2, {taps - 1}, {channels}] "
+                              "and the requests' phases")
         stride = state.stride(0)
     requests = cu_seqlens.numel() - 1
     _lib.check(_lib.load().oi_short_conv(out.data_ptr(), _code(out, "short_conv"), x.data_ptr(), _code(x, "short_conv"),
                                          weight.data_ptr(), _code(weight, "short_conv weight"), _ptr(state), stride,
-                                         cu_seqlens.data_ptr(), token_req.data_ptr(), state_slots.data_ptr(), tokens, requests,
+                                         cu_seqlens.data_ptr(), token_req.data_ptr(), state_slots.data_ptr(), _ptr(state_phase),
+                                         tokens, requests,
                                          channels, taps, 1 if add_input else 0, 1 if update_state else 0, _stream()), "short_conv")
     return out
 

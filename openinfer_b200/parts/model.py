@@ -354,6 +354,7 @@ class Model:
         step = native.BranchStepDesc(
             token_ids=ctx.token_ids.data_ptr(), attn_steps=steps, want_rows=ptr(row_idx) if n_want else 0,
             cu_seqlens=ctx.cu_seqlens.data_ptr(), token_req=ctx.token_req.data_ptr(), state_slots=ctx.state_slots.data_ptr(),
+            state_phase=ctx.state_phase.data_ptr(),
             h=h.data_ptr(), hist=ptr(hist), u=u.data_ptr(), low=ptr(low), proj=proj.data_ptr(), mixed=mixed.data_ptr(),
             branch=branch.data_ptr(), z=z.data_ptr(), wanted=ptr(wanted), logits=ptr(logits), tokens=T, requests=ctx.num_requests,
             num_attn_steps=len(keys), num_want=n_want)

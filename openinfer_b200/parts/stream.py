@@ -38,13 +38,15 @@ class ShortConv(Part):
 
     def state_needs(self) -> List[StateNeed]:
         s = self.spec
-        return [StateNeed((s.taps - 1, s.channels), "float32")] if s.taps > 1 else []
+        # two copies: the kernel reads a request's old state in its portion's first rows while it writes the new one
+        # from the last rows
+        return [StateNeed((s.taps - 1, s.channels), "float32", phases=2)] if s.taps > 1 else []
 
     def forward(self, x: torch.Tensor, ctx, state_ids, out_dtype: torch.dtype) -> torch.Tensor:
         """x [tokens, channels] (float32 or ``out_dtype``) -> x + conv(x) in ``out_dtype``; the state moves on."""
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         state = ctx.cache.state_tensor(state_ids[0]) if self.spec.taps > 1 else None
-        return ops.short_conv(out, x, self.weight, state, ctx.cu_seqlens, ctx.token_req, ctx.state_slots,
+        return ops.short_conv(out, x, self.weight, state, ctx.cu_seqlens, ctx.token_req, ctx.state_slots, ctx.state_phase,
                               add_input=self.spec.add_input)
 
 

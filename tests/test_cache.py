@@ -280,3 +280,28 @@ def test_prefix_cache_is_not_used_with_windows_or_state():
     cm2.add_state(StateNeed((3,)))
     cm2.allocate(8, 2)
     assert not cm2.prefix_usable()
+
+
+def test_two_phase_state_turns_over_when_a_step_is_committed_only():
+    """A state of two copies: the copy a request's next step reads changes with every committed step of that request,
+    not with a reservation that is rolled back, and not with other requests' steps."""
+    from openinfer_b200.cache.manager import CacheManager, KvNeed, StateNeed
+    cache = CacheManager(page_size=4)
+    cache.add_kv_layer(KvNeed(1, 8))
+    cache.add_state(StateNeed((3, 5), "float32", phases=2))
+    cache.allocate(16, 2)
+    cache.open("a")
+    cache.open("b")
+    assert cache.state_phase("a") == 0 and cache.state_phase("b") == 0
+    cache.reserve("a", 5)
+    cache.rollback("a")
+    assert cache.state_phase("a") == 0
+    cache.reserve("a", 5)
+    cache.commit("a")
+    assert cache.state_phase("a") == 1 and cache.state_phase("b") == 0
+    cache.reserve("a", 1)
+    cache.commit("a")
+    assert cache.state_phase("a") == 0
+    cache.close("a")
+    cache.open("c")
+    assert cache.state_phase("c") == 0

@@ -84,7 +84,7 @@ def test_cache_needs_one_plane_per_latent_and_windows_widened_by_readers():
     assert needs == [(1, 32, 50, 1, 1), (1, 40, None, 1, 1)]     # 36 numbers in rows of 40; readers share the owner's layer
     b = model.bindings
     assert [x.owns_kv for x in b] == [True, False, True, False] and b[1].kv == b[0].kv and b[3].kv == b[2].kv
-    assert [len(x.states) for x in b] == [1, 1, 1, 1] and [n.shape for n in cache.state_needs] == [(3, 64)] * 4
+    assert [len(x.states) for x in b] == [1, 1, 1, 1] and [(n.shape, n.phases) for n in cache.state_needs] == [((3, 64), 2)] * 4
     assert cache.bytes_per_page(0, 2) == 16 * 32 * 2             # one plane, not keys and values
     cache.allocate(8, 2)
     cache.open("r")

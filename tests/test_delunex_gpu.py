@@ -45,7 +45,7 @@ def _dev(t, dtype=None):
     return t.to(device="cuda", dtype=dtype or t.dtype)
 
 
-@pytest.mark.parametrize("taps,channels", [(1, 24), (2, 40), (3, 64), (5, 300)])
+@pytest.mark.parametrize("taps,channels", [(1, 24), (2, 40), (3, 64), (5, 300), (3, 30), (9, 32), (4, 1030)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_short_conv_kernel_portions_and_state(taps, channels, out_dtype):
     """Three requests in three steps of unequal portions (one token, fewer than taps - 1, many): every step's output
@@ -58,7 +58,7 @@ def test_short_conv_kernel_portions_and_state(taps, channels, out_dtype):
     want = [s + plain.causal_conv(s, w.double()) for s in seqs]
     cuts = [[1, 2, 8], [taps, 1, taps], [3, 3, 1]]                 # per request: its portions, step by step
     slots = [2, 0, 3]
-    state = torch.full((4, max(taps - 1, 1), channels), 7.0, device="cuda")[:, : taps - 1].contiguous()
+    state = torch.full((4, 2, max(taps - 1, 1), channels), 7.0, device="cuda")[:, :, : taps - 1].contiguous()
     state[slots] = 0                                               # an opened request's state is zero; slot 1 is someone else's
     at = [0, 0, 0]
     for step in range(3):
@@ -67,7 +67,12 @@ def test_short_conv_kernel_portions_and_state(taps, channels, out_dtype):
         cu = torch.tensor([0] + list(torch.tensor([r.shape[0] for r in rows]).cumsum(0)), dtype=torch.int32, device="cuda")
         req = torch.cat([torch.full((r.shape[0],), b, dtype=torch.int32) for b, r in enumerate(rows)]).cuda()
         out = torch.empty(x.shape, dtype=out_dtype, device="cuda")
-        ops.short_conv(out, x, _dev(w), state if taps > 1 else None, cu, req, torch.tensor(slots, dtype=torch.int32, device="cuda"))
+        # the two copies of a request's state take turns: its second request sits the first step's phase out of step
+        phase = torch.tensor([step & 1, (step + 1) & 1, step & 1], dtype=torch.int32, device="cuda")
+        if step == 0 and taps > 1:
+            state[0, 0].copy_(state[0, 1])                         # (request 1 starts in phase 1: its zeros are there already)
+        ops.short_conv(out, x, _dev(w), state if taps > 1 else None, cu, req, torch.tensor(slots, dtype=torch.int32, device="cuda"),
+                       phase if taps > 1 else None)
         ref = torch.cat([want[b][at[b]: at[b] + cuts[b][step]] for b in range(3)])
         tol = 1e-5 if out_dtype == torch.float32 else 2e-2
         assert (out.double().cpu() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
