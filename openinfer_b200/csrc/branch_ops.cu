@@ -289,18 +289,39 @@ __global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const TA* __re
 
 // kConvRows consecutive rows and four channels per thread: a row's earlier inputs stay in registers while the thread
 // walks down its rows (rows of one request are consecutive), the taps' weights are read once, and only a request's
-// first rows of the step go to its state
+// first rows of the step go to its state. The same launch leaves the new state: blocks behind the filter's own, one per
+// request, write the copy of the state that the step does not read.
 constexpr int kConvRows = 4;
 constexpr int kConvMaxTaps = 8;
 template <typename TX, typename TO, int kTaps>     // kTaps: 2, 4 or 8, at least the taps
 __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype, float* __restrict__ state,
-    long long state_stride, const int* __restrict__ token_req, const int* __restrict__ state_slots,
-    const int* __restrict__ state_phase, int tokens, int channels, int taps, int add_input, int update_state) {
+    long long state_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
+    const int* __restrict__ state_slots, const int* __restrict__ state_phase, int tokens, int channels, int taps, int add_input,
+    int conv_blocks) {
   pdl_trigger();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
-  const int t0 = blockIdx.x * kConvRows;
   const int keep = taps - 1;
+  if ((int)blockIdx.x >= conv_blocks) {
+    // The blocks behind the filter's own: one per request, they leave the state as it stands after the step in the copy
+    // that the step does not read (the filter's blocks read the other one, so the two kinds of block never meet).
+    pdl_wait();
+    const int b = blockIdx.x - conv_blocks;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    if (c >= channels || n <= 0 || token_req[start] < 0) return;   // a padding request of a recorded step owns no state
+    const int phase = state_phase[b];
+    const float* old = state + (size_t)state_slots[b] * state_stride + (size_t)phase * keep * channels;
+    float* nx = state + (size_t)state_slots[b] * state_stride + (size_t)(1 - phase) * keep * channels;
+    for (int k = 0; k < keep; ++k) {
+      const int s = n + k - keep;
+      float v[4];
+      if (s >= 0) load4(x + (size_t)(start + s) * channels + c, v);
+      else load4(old + (size_t)(k + n) * channels + c, v);
+      store4(nx + (size_t)k * channels + c, v);
+    }
+    return;
+  }
+  const int t0 = blockIdx.x * kConvRows;
   float wt[kTaps][4];
   if (c < channels) {
 #pragma unroll
@@ -320,16 +341,14 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     if (j < keep && r >= 0) load4(x + (size_t)r * channels + c, ring[j]);
   }
   const int t_end = min(tokens, t0 + kConvRows);
-  // The requests of the rows, of the taps - 1 rows above and of the taps - 1 rows below them, and the rows' inputs: all
-  // asked for before any is used. A request's rows are consecutive, so a row's place in its portion (from the front
-  // and from the end) shows in its neighbours' requests alone.
-  constexpr int kSpan = kConvRows + 2 * (kTaps - 1);
-  int reqs[kSpan];
+  // The requests of the rows and of the taps - 1 rows above them, and the rows' inputs: all asked for before any is used.
+  // A request's rows are consecutive, so a row's place in its portion shows in its neighbours' requests alone.
+  int reqs[kConvRows + kTaps - 1];
   float curs[kConvRows][4];
 #pragma unroll
-  for (int i = 0; i < kSpan; ++i) {
+  for (int i = 0; i < kConvRows + kTaps - 1; ++i) {
     const int r = t0 - (kTaps - 1) + i;
-    reqs[i] = (r >= 0 && r < tokens && r >= t0 - keep && r < t_end + keep) ? token_req[r] : -2;
+    reqs[i] = (r >= 0 && r < t_end && r >= t0 - keep) ? token_req[r] : -2;
   }
 #pragma unroll
   for (int i = 0; i < kConvRows; ++i)
@@ -339,18 +358,13 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     const int t = t0 + i;
     if (t >= t_end) break;
     const int req = reqs[i + kTaps - 1];
-    int rel = 0, after = 0;      // rows of the same request directly above / below, counted up to taps - 1
+    int rel = 0;                 // rows of the same request directly above, counted up to taps - 1
 #pragma unroll
-    for (int j = 1; j < kTaps; ++j) {
+    for (int j = 1; j < kTaps; ++j)
       if (j <= keep && rel == j - 1 && reqs[i + kTaps - 1 - j] == req) rel = j;
-      if (j <= keep && after == j - 1 && reqs[i + kTaps - 1 + j] == req) after = j;
-    }
-    // the request's state: the copy this step reads, and the one it leaves behind
-    const bool touches = req >= 0 && keep > 0 && (rel < keep || (update_state && after < keep));
-    float* base = touches ? state + (size_t)state_slots[req] * state_stride : nullptr;
-    const int phase = touches ? state_phase[req] : 0;
-    const float* st = base ? base + (size_t)phase * keep * channels : nullptr;
-    float* nx = (base && update_state) ? base + (size_t)(1 - phase) * keep * channels : nullptr;
+    // a portion's first rows read the copy of the request's state that is current in this step
+    const float* st = (req >= 0 && rel < keep)
+                          ? state + (size_t)state_slots[req] * state_stride + (size_t)state_phase[req] * keep * channels : nullptr;
     float cur[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) cur[e] = curs[i][e];
@@ -374,19 +388,6 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
       for (int e = 0; e < 4; ++e) acc[e] += wt[j][e] * v[e];
     }
     store4(out + (size_t)t * channels + c, acc);
-    if (nx != nullptr && after < keep) {
-      // one of the portion's last taps - 1 rows: its input is entry keep - 1 - after of the state left behind
-      store4(nx + (size_t)(keep - 1 - after) * channels + c, cur);
-      if (rel == 0 && after + 1 < keep) {
-        // the portion's first row, and the portion (after + 1 rows) is shorter than the state: the old entries move up
-        const int n = after + 1;
-        for (int k = 0; k < keep - n; ++k) {
-          float v[4];
-          load4(st + (size_t)(k + n) * channels + c, v);
-          store4(nx + (size_t)k * channels + c, v);
-        }
-      }
-    }
 #pragma unroll
     for (int j = kTaps - 1; j > 0; --j) {
 #pragma unroll
@@ -530,10 +531,12 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
   const bool vec = channels % 4 == 0 && taps <= kConvMaxTaps && aligned16(out) && aligned16(x) &&
                    (taps == 1 || (aligned16(state) && state_stride % 4 == 0));
   const int vthreads = channels / 4 >= 256 ? 256 : ((channels / 4 + 31) / 32) * 32;
-  const dim3 vgrid((tokens + kConvRows - 1) / kConvRows, vec ? (channels / 4 + vthreads - 1) / vthreads : 1);
+  // the filter's blocks, and behind them one block per request (and chunk of channels) that leaves the new state
+  const int conv_blocks = (tokens + kConvRows - 1) / kConvRows;
+  const dim3 vgrid(conv_blocks + ((update_state && taps > 1) ? requests : 0), vec ? (channels / 4 + vthreads - 1) / vthreads : 1);
 #define OI_CONV_VEC(TX, TO, KT)                                                                                          \
   oi_launch(short_conv_vec_kernel<TX, TO, KT>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, state, state_stride, \
-            token_req, state_slots, state_phase, tokens, channels, taps, add_input, update_state)
+            cu_seqlens, token_req, state_slots, state_phase, tokens, channels, taps, add_input, conv_blocks)
 #define OI_CONV_CASE(XD, OD, TX, TO)                                                                                     \
   if (x_dtype == XD && out_dtype == OD) {                                                                                \
     if (vec) {                                                                                                           \
