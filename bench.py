@@ -17,6 +17,10 @@ tokens beside 56 decoding requests, device-timed and through ``LLM.step()``) and
 sizes (decode at batch 1/8/64, prefill), each with its own roofline fractions and clock
 sample. Prints ONE JSON line. The engine runs on one GPU: for --gpus > 1 it says so and
 exits with 2.
+
+``--design delunex`` measures something else and leaves the above as it is: the Delunex design at layer sizes of
+real models beside Qwen3 at equal sizes (decode at batch 1 / 8 / 64, a 2,048-token prefill, with ``--design-kernels``
+every kernel's time per step), one JSON line of its own.
 """
 from __future__ import annotations
 
@@ -417,7 +421,7 @@ def design_configs(key, layers=None):
     width, n_layers, heads, window, ff, inter = DESIGN_SIZES[key]
     n_layers = layers or n_layers
     mixer = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 128, "scale": 128 ** -0.5, "mask": {"size": window}}
-    # as in small models of this design: two of every three layers read the latent of the layer before them
+    # the design shares latents between layers: here two of every three layers read the latent of the layer before them
     lay = []
     for i in range(n_layers):
         m = dict(mixer)
