@@ -11,10 +11,11 @@ from .base import (
     unregister_architecture,
 )
 from .delunex import DelunexConfig
+from .pilonex import PilonexConfig
 from .qwen3 import Qwen3Config
 
 __all__ = [
-    "ArchitectureEntry", "ConfigError", "DelunexConfig", "ModelConfig", "Qwen3Config", "known_architectures",
+    "ArchitectureEntry", "ConfigError", "DelunexConfig", "ModelConfig", "PilonexConfig", "Qwen3Config", "known_architectures",
     "load_config", "read_config_json", "register_architecture", "resolve_architecture",
     "unregister_architecture",
 ]

@@ -99,7 +99,8 @@ template <typename TX, typename TO>
 __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype,
                                   const float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ token_req, const int* __restrict__ state_slots,
-                                  const int* __restrict__ state_phase, int channels, int taps, int add_input) {
+                                  const int* __restrict__ state_phase, int channels, int taps, int add_input,
+                                  long long x_stride, long long out_stride, int act) {
   pdl_start();
   const int t = blockIdx.x;
   const int req = token_req[t];
@@ -109,18 +110,19 @@ __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x
   const float* st = (req >= 0 && keep > 0) ? state + (size_t)state_slots[req] * state_stride + (size_t)state_phase[req] * keep * channels
                                            : nullptr;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-    const float cur = to_f32(x[(size_t)t * channels + c]);
+    const float cur = to_f32(x[(size_t)t * x_stride + c]);
     float acc = add_input ? cur : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int s = rel - keep + j;
       float v;
       if (s >= 0)
-        v = to_f32(x[(size_t)(start + s) * channels + c]);
+        v = to_f32(x[(size_t)(start + s) * x_stride + c]);
       else
         v = st ? st[(size_t)(keep + s) * channels + c] : 0.f;
       acc += load_as_f32(w, w_dtype, (size_t)c * taps + j) * v;
     }
-    out[(size_t)t * channels + c] = from_f32<TO>(acc);
+    if (act == OI_ACT_SILU) acc = acc / (1.f + expf(-acc));
+    out[(size_t)t * out_stride + c] = from_f32<TO>(acc);
   }
 }
 
@@ -129,7 +131,7 @@ template <typename TX>
 __global__ void short_conv_state_kernel(float* __restrict__ state, long long state_stride, const TX* __restrict__ x,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
                                         const int* __restrict__ state_slots, const int* __restrict__ state_phase, int channels,
-                                        int keep) {
+                                        int keep, long long x_stride) {
   pdl_start();
   const int b = blockIdx.x;
   const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
@@ -140,7 +142,7 @@ __global__ void short_conv_state_kernel(float* __restrict__ state, long long sta
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     for (int k = 0; k < keep; ++k) {
       const int s = n + k - keep;
-      st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * channels + c]) : old[(size_t)(k + n) * channels + c];
+      st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * x_stride + c]) : old[(size_t)(k + n) * channels + c];
     }
   }
 }
@@ -516,10 +518,14 @@ OI_API int oi_history_average(float* h, float* hist, long long hist_stride, int 
   return OI_OK;
 }
 
-OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float* state,
-                         long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots,
-                         const int* state_phase, int tokens, int requests, int channels, int taps, int add_input, int update_state,
-                         void* stream) {
+// x_stride / out_stride: elements between rows (the channels of a row may be a slice of a wider buffer); act: OI_ACT_NONE
+// or OI_ACT_SILU on the filter's result. The state keeps the INPUTS, so the activation does not touch it.
+OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride, const void* x, int x_dtype, long long x_stride,
+                                 const void* w, int w_dtype, float* state, long long state_stride, const int* cu_seqlens,
+                                 const int* token_req, const int* state_slots, const int* state_phase, int tokens, int requests,
+                                 int channels, int taps, int add_input, int update_state, int act, void* stream) {
+  OI_REQUIRE(act == OI_ACT_NONE || act == OI_ACT_SILU, "short_conv: unknown activation code %d", act);
+  OI_REQUIRE(x_stride >= channels && out_stride >= channels, "short_conv: rows narrower than the channels");
   OI_REQUIRE(tokens >= 0 && requests >= 0 && channels > 0 && taps >= 1, "short_conv: bad sizes tokens=%d channels=%d taps=%d",
              tokens, channels, taps);
   OI_REQUIRE(taps == 1 || (state != nullptr && state_phase != nullptr && state_stride >= 2LL * (taps - 1) * channels),
@@ -528,7 +534,8 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
   cudaStream_t s = (cudaStream_t)stream;
   const int cy = (channels + kRowThreads - 1) / kRowThreads;
   const dim3 grid(tokens, cy);
-  const bool vec = channels % 4 == 0 && taps <= kConvMaxTaps && aligned16(out) && aligned16(x) &&
+  const bool vec = act == OI_ACT_NONE && x_stride == channels && out_stride == channels && channels % 4 == 0 &&
+                   taps <= kConvMaxTaps && aligned16(out) && aligned16(x) &&
                    (taps == 1 || (aligned16(state) && state_stride % 4 == 0));
   const int vthreads = channels / 4 >= 256 ? 256 : ((channels / 4 + 31) / 32) * 32;
   // the filter's blocks, and behind them one block per request (and chunk of channels) that leaves the new state
@@ -547,11 +554,12 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
       return OI_OK;                                                                                                      \
     }                                                                                                                    \
     oi_launch(short_conv_kernel<TX, TO>, grid, kRowThreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, (const float*)state, \
-              state_stride, cu_seqlens, token_req, state_slots, state_phase, channels, taps, add_input);                 \
+              state_stride, cu_seqlens, token_req, state_slots, state_phase, channels, taps, add_input, x_stride,        \
+              out_stride, act);                                                                                          \
     OI_CHECK_LAUNCH();                                                                                                   \
     if (update_state && taps > 1) {                                                                                      \
       oi_launch(short_conv_state_kernel<TX>, dim3(requests, cy), kRowThreads, 0, s, state, state_stride, (const TX*)x,    \
-                cu_seqlens, token_req, state_slots, state_phase, channels, taps - 1);                                    \
+                cu_seqlens, token_req, state_slots, state_phase, channels, taps - 1, x_stride);                          \
       OI_CHECK_LAUNCH();                                                                                                 \
     }                                                                                                                    \
     return OI_OK;                                                                                                        \
@@ -562,6 +570,14 @@ OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, c
 #undef OI_CONV_CASE
 #undef OI_CONV_VEC
   OI_REQUIRE(false, "short_conv: dtype codes %d -> %d are not supported", x_dtype, out_dtype);
+}
+
+OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float* state,
+                         long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots,
+                         const int* state_phase, int tokens, int requests, int channels, int taps, int add_input, int update_state,
+                         void* stream) {
+  return oi_short_conv_strided(out, out_dtype, channels, x, x_dtype, channels, w, w_dtype, state, state_stride, cu_seqlens, token_req,
+                               state_slots, state_phase, tokens, requests, channels, taps, add_input, update_state, OI_ACT_NONE, stream);
 }
 
 OI_API int oi_latent_store(void* pages, long long page_stride, int page_size, int row_elems, const void* src, long long src_stride,

@@ -132,6 +132,18 @@ __device__ __forceinline__ float gate_act(float g, int act) {
   return kFast ? __fdividef(g, 1.f + __expf(-t)) : g / (1.f + expf(-t));
 }
 
+// Gated activations that also shape the up value. OI_ACT_SWIGLU_CLAMP: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit)
+// and u' = clamp(u, -limit, limit); the limit travels with the code. The other codes are act(g) * u.
+#define OI_ACT_SWIGLU_CLAMP 4
+template <bool kFast>
+__device__ __forceinline__ float glu_act(float g, float u, int act, float limit) {
+  if (act != OI_ACT_SWIGLU_CLAMP) return gate_act<kFast>(g, act) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  const float t = 1.702f * g;
+  return (kFast ? __fdividef(g, 1.f + __expf(-t)) : g / (1.f + expf(-t))) * (u + 1.f);
+}
+
 // Activations of ONE argument, applied to a product's sums where they are complete (the codes continue the gate
 // activations'). OI_ACT_XIELU: a_p x^2 + x / 2 above zero, a_n (e^x - 1 - x) + x / 2 below, with the two numbers given.
 #define OI_ACT_XIELU 3

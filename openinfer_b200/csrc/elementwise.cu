@@ -340,20 +340,21 @@ OI_API int oi_scale_cap(void* x, int dtype, long long n, float scale, float cap,
 // holds a gate block and its up block side by side can form the activation in its epilogue.)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n, int act) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n, int act,
+                                float limit) {
   pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i - r * inter;
     const size_t gi = r * 2 * inter + (c / block) * 2 * block + (c % block);
     const float g = to_f32(gate_up[gi]);
     const float u = to_f32(gate_up[gi + block]);
-    out[i] = from_f32<T>(gate_act<false>(g, act) * u);
+    out[i] = from_f32<T>(glu_act<false>(g, u, act, limit));
   }
 }
 
 // 8 bf16 per thread when inter and block are multiples of 8
 __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up,
-                                       int inter8, int block8, size_t n8, int act) {
+                                       int inter8, int block8, size_t n8, int act, float limit) {
   pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter8, c = i - r * inter8;
@@ -368,14 +369,15 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __r
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]);
       const float2 u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(gate_act<false>(g.x, act) * u.x, gate_act<false>(g.y, act) * u.y);
+      o2[k] = __floats2bfloat162_rn(glu_act<false>(g.x, u.x, act, limit), glu_act<false>(g.y, u.y, act, limit));
     }
     out[i] = ov;
   }
 }
 
-OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, void* stream) {
-  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH, "silu_mul: unknown activation code %d", act);
+// out[r, i] = act(gate_i, up_i) for every gated activation, the ones with a limit included (oi_silu_mul: the two without)
+OI_API int oi_glu_act(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, float limit, void* stream) {
+  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH || act == OI_ACT_SWIGLU_CLAMP, "glu_act: unknown activation code %d", act);
   OI_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
   OI_REQUIRE(block > 0 && inter % block == 0, "silu_mul: block %d does not divide inter %d", block, inter);
   if (rows == 0) return OI_OK;
@@ -384,13 +386,18 @@ OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int 
   if (dtype == OI_BF16 && inter % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
     const size_t n8 = n / 8;
     const int blocks = (int)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
-    oi_launch(silu_mul_bf16x8_kernel, blocks, 256, 0, s, (uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8, act);
+    oi_launch(silu_mul_bf16x8_kernel, blocks, 256, 0, s, (uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8, act, limit);
   } else {
     const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-    if (dtype == OI_F32) oi_launch(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, inter, block, n, act);
-    else if (dtype == OI_BF16) oi_launch(silu_mul_kernel<bf16>, blocks, 256, 0, s, (bf16*)out, (const bf16*)gate_up, inter, block, n, act);
+    if (dtype == OI_F32) oi_launch(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, inter, block, n, act, limit);
+    else if (dtype == OI_BF16) oi_launch(silu_mul_kernel<bf16>, blocks, 256, 0, s, (bf16*)out, (const bf16*)gate_up, inter, block, n, act, limit);
     else OI_REQUIRE(false, "silu_mul: unknown dtype code %d", dtype);
   }
   OI_CHECK_LAUNCH();
   return OI_OK;
+}
+
+OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, void* stream) {
+  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH, "silu_mul: unknown activation code %d", act);
+  return oi_glu_act(out, gate_up, dtype, rows, inter, block, act, 0.f, stream);
 }

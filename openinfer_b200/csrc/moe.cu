@@ -1,0 +1,292 @@
+// Routed experts: a feed-forward of `experts` small gated layers of which every row uses `top`.
+//
+//   1. moe_router_kernel   z = W_r x in float32 (one warp a row), the `top` largest logits (ties to the lower index),
+//                          their softmax -> ids [rows, top], weights [rows, top]
+//   2. moe_group_kernel    the (row, choice) pairs sorted by expert (stable, so the order never depends on timing), and
+//                          the list of row tiles (expert, first sorted place, rows) the products run over
+//   3. moe_gemm_kernel     per tile: act(x W_gate_e^T, x W_up_e^T) for the rows of the tile, gathered by their pair's row;
+//                          then the down projection, each row written to its pair's place
+//   4. moe_combine_kernel  out[row] = sum_j weight[row, j] * y[row * top + j], j ascending
+//
+// Everything a step needs is found on the device (no sizes travel back to the host), so a step of single tokens can be
+// recorded and replayed. A row's sums are formed in ascending k whatever else shares its tile: the result of a row does
+// not depend on the batch. The products add up in float32 on the ordinary pipes.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileM = 32, kTileN = 64, kTileK = 16;
+constexpr int kMaxTop = 32;
+
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w, int w_dtype, int rows, int K,
+                                  int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
+  pdl_start();
+  extern __shared__ float smem[];
+  const int warps = blockDim.x >> 5, wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* z = smem + (size_t)wi * E;
+  unsigned char* taken = reinterpret_cast<unsigned char*>(smem + (size_t)warps * E) + (size_t)wi * E;
+  const int row = blockIdx.x * warps + wi;
+  if (row >= rows) return;
+  const T* xr = x + (size_t)row * ldx;
+  for (int e = 0; e < E; ++e) {
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc += load_as_f32(w, w_dtype, (size_t)e * K + k) * to_f32(xr[k]);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      z[e] = acc;
+      taken[e] = 0;
+    }
+  }
+  __syncwarp();
+  float chosen_z[kMaxTop];
+  int chosen_e[kMaxTop];
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      if (taken[e]) continue;
+      const float v = z[e];
+      if (be == 0x7fffffff || v > best) {
+        best = v;
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > best || (ov == best && oe < be))) {
+        best = ov;
+        be = oe;
+      }
+    }
+    if (lane == 0) taken[be] = 1;
+    __syncwarp();
+    chosen_z[j] = best;
+    chosen_e[j] = be;
+  }
+  if (lane == 0) {
+    float mx = chosen_z[0], sum = 0.f;
+    for (int j = 1; j < top; ++j) mx = fmaxf(mx, chosen_z[j]);
+    for (int j = 0; j < top; ++j) {
+      chosen_z[j] = expf(chosen_z[j] - mx);
+      sum += chosen_z[j];
+    }
+    for (int j = 0; j < top; ++j) {
+      ids[(size_t)row * top + j] = chosen_e[j];
+      wts[(size_t)row * top + j] = chosen_z[j] / sum;
+    }
+  }
+}
+
+// One block per expert e. sorted[first_e + i] = the i-th pair (in ascending pair number) that chose e; tiles of kTileM
+// sorted places that belong to one expert: tile_info[3 * t] = expert, first place, rows. tile_info's last word
+// (at 3 * max_tiles) is the number of tiles.
+__global__ void moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ sorted, int* __restrict__ tile_info,
+                                 int max_tiles) {
+  pdl_start();
+  extern __shared__ int hist[];       // [E] counts, then [warps] scan scratch
+  __shared__ int s_first, s_tile0, s_count;
+  const int e = blockIdx.x;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int id = ids[p];
+    if (id >= 0 && id < E) atomicAdd(&hist[id], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int first = 0, tile0 = 0, total = 0;
+    for (int i = 0; i < E; ++i) {
+      const int tiles = (hist[i] + kTileM - 1) / kTileM;
+      if (i < e) {
+        first += hist[i];
+        tile0 += tiles;
+      }
+      total += tiles;
+    }
+    s_first = first, s_tile0 = tile0, s_count = hist[e];
+    if (e == 0) tile_info[3 * max_tiles] = total < max_tiles ? total : max_tiles;
+  }
+  __syncthreads();
+  const int first = s_first, tile0 = s_tile0, count = s_count;
+  for (int t = threadIdx.x; t * kTileM < count; t += blockDim.x) {
+    if (tile0 + t < max_tiles) {
+      tile_info[3 * (tile0 + t)] = e;
+      tile_info[3 * (tile0 + t) + 1] = first + t * kTileM;
+      tile_info[3 * (tile0 + t) + 2] = count - t * kTileM < kTileM ? count - t * kTileM : kTileM;
+    }
+  }
+  // stable compaction of the pairs that chose e
+  int* wsum = hist + E;
+  const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  int running = 0;
+  for (int base = 0; base < pairs; base += blockDim.x) {
+    const int p = base + threadIdx.x;
+    const bool mine = p < pairs && ids[p] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    __syncthreads();
+    if (lane == 0) wsum[wi] = __popc(ballot);
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int w = 0; w < warps; ++w) {
+      if (w < wi) before += wsum[w];
+      all += wsum[w];
+    }
+    if (mine) sorted[first + running + before + __popc(ballot & ((1u << lane) - 1))] = p;
+    running += all;
+  }
+}
+
+// out rows of one tile: C[i, n] = sum_k A[src(i), k] * W_e[n, k] (k ascending), i over the tile's sorted places.
+// kGlu: W_e holds N gate rows and then N up rows; the result is g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit),
+// u' = clamp(u, -limit, limit). a_div: the source row of place i is sorted[i] / a_div (a_div 0: the place itself).
+// scatter: the result of place i goes to row sorted[i] (else to row i).
+template <typename T, typename TO, bool kGlu>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, long long lda, int a_div, const T* __restrict__ Wt,
+                                                       long long w_expert_stride, TO* __restrict__ out, long long ld_out, int scatter,
+                                                       const int* __restrict__ sorted, const int* __restrict__ tile_info,
+                                                       int max_tiles, int N, int K, float limit) {
+  pdl_start();
+  const int tile = blockIdx.x;
+  if (tile >= tile_info[3 * max_tiles]) return;
+  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = tile_info[3 * tile + 2];
+  const int n0 = blockIdx.y * kTileN;
+  __shared__ float As[kTileK][kTileM + 1];
+  __shared__ float Wg[kTileK][kTileN + 1];
+  __shared__ float Wu[kGlu ? kTileK : 1][kTileN + 1];
+  __shared__ int src[kTileM];
+  if (threadIdx.x < kTileM) {
+    int r = -1;
+    if ((int)threadIdx.x < m_rows) {
+      const int place = place0 + threadIdx.x;
+      r = a_div > 0 ? sorted[place] / a_div : place;
+    }
+    src[threadIdx.x] = r;
+  }
+  __syncthreads();
+  const T* We = Wt + (size_t)e * w_expert_stride;
+  const int tn = threadIdx.x % 16, tm = threadIdx.x / 16;   // thread: rows tm, tm + 16; columns tn + 16 j, j < 4
+  float acc[2][4] = {}, accu[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    for (int i = threadIdx.x; i < kTileM * kTileK; i += 256) {
+      const int m = i / kTileK, k = i % kTileK;
+      const int r = src[m];
+      As[k][m] = (r >= 0 && k0 + k < K) ? to_f32(A[(size_t)r * lda + k0 + k]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < kTileN * kTileK; i += 256) {
+      const int n = i / kTileK, k = i % kTileK;
+      const bool ok = n0 + n < N && k0 + k < K;
+      Wg[k][n] = ok ? to_f32(We[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+      if (kGlu) Wu[k][n] = ok ? to_f32(We[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kTileK; ++k) {
+      const float a0 = As[k][tm], a1 = As[k][tm + 16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w = Wg[k][tn + 16 * j];
+        acc[0][j] += a0 * w;
+        acc[1][j] += a1 * w;
+        if (kGlu) {
+          const float u = Wu[k][tn + 16 * j];
+          accu[0][j] += a0 * u;
+          accu[1][j] += a1 * u;
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = tm + 16 * i;
+    if (m >= m_rows) continue;
+    const int place = place0 + m;
+    const size_t row = scatter ? (size_t)sorted[place] : (size_t)place;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tn + 16 * j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (kGlu) {
+        const float g = fminf(v, limit), u = fminf(fmaxf(accu[i][j], -limit), limit);
+        v = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+      }
+      out[row * ld_out + n] = from_f32<TO>(v);
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts, int top, int W,
+                                   size_t n) {
+  pdl_start();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / W, c = i - t * W;
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) acc += wts[t * top + j] * y[(t * top + j) * W + c];
+    out[i] = acc;
+  }
+}
+
+}  // namespace
+
+OI_API int oi_moe_max_tiles(int pairs, int experts) { return pairs / kTileM + experts; }
+
+// x [rows, K] (row stride ldx) in `dtype`; router weights [E, K]; ids, wts [rows, top]; sorted [rows * top];
+// tile_info [3 * max_tiles + 1] with max_tiles = oi_moe_max_tiles(rows * top, E).
+OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int E, int top,
+                        int* ids, float* wts, int* sorted, int* tile_info, void* stream) {
+  OI_REQUIRE(rows >= 0 && K > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route: bad sizes experts=%d top=%d (at most %d)", E,
+             top, kMaxTop);
+  OI_REQUIRE(E <= 4096, "moe_route: %d experts, at most 4096", E);
+  if (rows == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float) + (size_t)warps * E + 16;
+  if (dtype == OI_F32)
+    oi_launch(moe_router_kernel<float>, (rows + warps - 1) / warps, warps * 32, smem, s, (const float*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+  else if (dtype == OI_BF16)
+    oi_launch(moe_router_kernel<bf16>, (rows + warps - 1) / warps, warps * 32, smem, s, (const bf16*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+  else
+    OI_REQUIRE(false, "moe_route: unknown dtype code %d", dtype);
+  OI_CHECK_LAUNCH();
+  const int pairs = rows * top;
+  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E));
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// act [rows * top, F] (scratch, `dtype`), y [rows * top, W] float32 (scratch), out [rows, W] float32.
+// w_gate_up [E, 2 F, W] (F gate rows, then F up rows), w_down [E, W, F], both in `dtype`.
+OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows, int W, int F,
+                          int E, int top, float limit, const int* sorted, const int* tile_info, const float* wts, void* act, float* y,
+                          float* out, void* stream) {
+  OI_REQUIRE(rows >= 0 && W > 0 && F > 0 && E > 0 && top > 0, "moe_experts: bad sizes");
+  if (rows == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int pairs = rows * top, max_tiles = oi_moe_max_tiles(pairs, E);
+  const dim3 g1(max_tiles, (F + kTileN - 1) / kTileN), g2(max_tiles, (W + kTileN - 1) / kTileN);
+  if (dtype == OI_F32) {
+    oi_launch(moe_gemm_kernel<float, float, true>, g1, 256, 0, s, (const float*)x, ldx, top, (const float*)w_gate_up, (long long)2 * F * W,
+              (float*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+    OI_CHECK_LAUNCH();
+    oi_launch(moe_gemm_kernel<float, float, false>, g2, 256, 0, s, (const float*)act, (long long)F, 0, (const float*)w_down, (long long)W * F,
+              y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+  } else if (dtype == OI_BF16) {
+    oi_launch(moe_gemm_kernel<bf16, bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
+              (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+    OI_CHECK_LAUNCH();
+    oi_launch(moe_gemm_kernel<bf16, float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
+              y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+  } else {
+    OI_REQUIRE(false, "moe_experts: unknown dtype code %d", dtype);
+  }
+  OI_CHECK_LAUNCH();
+  const size_t n = (size_t)rows * W;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  oi_launch(moe_combine_kernel, blocks, 256, 0, s, out, (const float*)y, wts, top, W, n);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}

@@ -58,6 +58,16 @@ _SIGNATURES = {
     "oi_latent_store": [P, L, I, I, P, L, I, P, I, P, I, I, F, F, P],
     "oi_head_gate": [P, L, P, L, I, I, I, I, P],
     "oi_xielu": [P, P, I, P, I, L, P],
+    "oi_short_conv_strided": [P, I, L, P, I, L, P, I, P, L, P, P, P, P, I, I, I, I, I, I, I, P],
+    "oi_glu_act": [P, P, I, I, I, I, I, F, P],
+    "oi_recurrent_scan": [I, P, L, I, I, I, P, L, I, I, P, L, P, P, I, F, F, P, L, P, P, P, P, P, L, I, I, I, I, I, P],
+    "oi_head_norm_gate": [P, I, L, P, L, P, L, P, I, I, I, I, I, F, F, P],
+    "oi_hyper_step": [P, I, I, I, P, P, F, F, P, P, P, I, P, I, F, F, P, I, P, P],
+    "oi_hyper_fanout": [P, P, I, I, I, I, P],
+    "oi_scaled_sum": [P, P, P, F, F, L, P],
+    "oi_moe_max_tiles": [I, I],
+    "oi_moe_route": [P, I, L, P, I, I, I, I, I, P, P, P, P, P],
+    "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, P, P, P, P, P, P, P],
 }
 
 

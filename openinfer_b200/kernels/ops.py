@@ -468,3 +468,188 @@ def xielu(out: torch.Tensor, x: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
     _lib.check(_lib.load().oi_xielu(out.data_ptr(), x.data_ptr(), _code(x, "xielu"), pq.data_ptr(), _code(pq, "xielu pq"),
                                     x.numel(), _stream()), "xielu")
     return out
+
+
+def glu_act(out: torch.Tensor, gate_up: torch.Tensor, block: Optional[int] = None, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """``silu_mul`` for every gated activation, the ones with a limit included ("swiglu_clamp": g' sigmoid(1.702 g')
+    (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit))."""
+    _cuda(out, gate_up)
+    rows, inter = out.shape
+    block = inter if block is None else int(block)
+    if gate_up.shape != (rows, 2 * inter) or out.dtype != gate_up.dtype or not (out.is_contiguous() and gate_up.is_contiguous()):
+        raise KernelError(f"glu_act: shapes out={tuple(out.shape)} gate_up={tuple(gate_up.shape)}")
+    _lib.check(_lib.load().oi_glu_act(out.data_ptr(), gate_up.data_ptr(), _code(out, "glu_act"), rows, inter, block, glu_code(act),
+                                      float(limit), _stream()), "glu_act")
+    return out
+
+
+# gated activations: the two of ACTIVATIONS and those that take a limit
+GLU_ACTIVATIONS = dict(ACTIVATIONS, swiglu_clamp=4)
+
+
+def glu_code(name: str) -> int:
+    try:
+        return GLU_ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"gated activation {name!r} has no kernel (known: {', '.join(sorted(GLU_ACTIVATIONS))})") from None
+
+
+def short_conv_act(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], cu_seqlens: torch.Tensor,
+                   token_req: torch.Tensor, state_slots: torch.Tensor, state_phase: Optional[torch.Tensor], *, act: str = "none",
+                   add_input: bool = False) -> torch.Tensor:
+    """``short_conv`` on a slice of columns of wider buffers (x and out [tokens, channels] with free row strides) and
+    with an activation on the filter's result ("none" or "silu")."""
+    _cuda(out, x, weight, state, cu_seqlens, token_req, state_slots, state_phase)
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    if out.shape != x.shape or weight.shape[0] != channels or x.stride(1) != 1 or out.stride(1) != 1 or not weight.is_contiguous():
+        raise KernelError(f"short_conv_act: shapes x={tuple(x.shape)} out={tuple(out.shape)} weight={tuple(weight.shape)}")
+    stride = 0
+    if taps > 1:
+        if (state is None or state.dtype != torch.float32 or state.shape[1:] != (2, taps - 1, channels) or not state.is_contiguous()
+                or state_phase is None):
+            raise KernelError(f"short_conv_act: {taps} taps need a contiguous float32 state [slots, 2, {taps - 1}, {channels}]")
+        stride = state.stride(0)
+    _lib.check(_lib.load().oi_short_conv_strided(
+        out.data_ptr(), _code(out, "short_conv"), out.stride(0), x.data_ptr(), _code(x, "short_conv"), x.stride(0), weight.data_ptr(),
+        _code(weight, "short_conv weight"), _ptr(state), stride, cu_seqlens.data_ptr(), token_req.data_ptr(), state_slots.data_ptr(),
+        _ptr(state_phase), tokens, cu_seqlens.numel() - 1, channels, taps, 1 if add_input else 0, 1,
+        {"none": 0, "silu": 1}[act], _stream()), "short_conv_act")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# recurrent mixers with a matrix memory per head (csrc/recurrent.cu)
+# ---------------------------------------------------------------------------
+SCAN_MATRIX_MEMORY, SCAN_GATED_DELTA = 0, 1
+
+
+def recurrent_scan(mode: int, out: torch.Tensor, qkv: torch.Tensor, offsets, gates: torch.Tensor, gate_offsets, state: torch.Tensor,
+                   ctx, heads: int, kv_heads: int, dim: int, vdim: int, *, p0: torch.Tensor, p1: torch.Tensor,
+                   decay: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0) -> torch.Tensor:
+    """The rows of a step through a matrix memory, request by request (see csrc/recurrent.cu). ``qkv`` and ``gates`` are
+    float32 [tokens, *] buffers read at the column ``offsets`` (q, k, v) and ``gate_offsets``; ``state`` float32
+    [slots, 2, heads, elems]; ``out`` float32 [tokens, heads * vdim]."""
+    _cuda(out, qkv, gates, state, p0, p1, decay)
+    for t in (out, qkv, gates, state, decay):
+        if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1):
+            raise KernelError("recurrent_scan: the buffers must be float32 rows")
+    elems = dim * vdim + (dim + 1 if mode == SCAN_MATRIX_MEMORY else 0)
+    if state.shape[1:] != (2, heads, elems) or not state.is_contiguous() or p0.dtype != p1.dtype:
+        raise KernelError(f"recurrent_scan: state {tuple(state.shape)} is not [slots, 2, {heads}, {elems}]")
+    _lib.check(_lib.load().oi_recurrent_scan(
+        mode, qkv.data_ptr(), qkv.stride(0), int(offsets[0]), int(offsets[1]), int(offsets[2]), gates.data_ptr(), gates.stride(0),
+        int(gate_offsets[0]), int(gate_offsets[1]), _ptr(decay), 0 if decay is None else decay.stride(0), p0.data_ptr(), p1.data_ptr(),
+        _code(p0, "recurrent_scan"), float(cap), float(q_scale), state.data_ptr(), state.stride(0), ctx.cu_seqlens.data_ptr(),
+        ctx.token_req.data_ptr(), ctx.state_slots.data_ptr(), ctx.state_phase.data_ptr(), out.data_ptr(), out.stride(0),
+        ctx.num_requests, heads, kv_heads, dim, vdim, _stream()), "recurrent_scan")
+    return out
+
+
+def head_norm_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int, vdim: int, eps: float,
+                   *, weight_per_head: bool, scale: float = 1.0) -> torch.Tensor:
+    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * sigmoid(gate[t, h, :]) * scale; o and gate float32 rows,
+    ``weight`` [heads * vdim] (``weight_per_head``) or [vdim] shared by the heads."""
+    _cuda(out, o, gate, weight)
+    if o.dtype != torch.float32 or gate.dtype != torch.float32 or o.stride(1) != 1 or gate.stride(1) != 1 or out.stride(1) != 1 \
+            or weight.numel() != (heads * vdim if weight_per_head else vdim) or not weight.is_contiguous():
+        raise KernelError("head_norm_gate: o and gate must be float32 rows and the weight of the stated size")
+    _lib.check(_lib.load().oi_head_norm_gate(out.data_ptr(), _code(out, "head_norm_gate"), out.stride(0), o.data_ptr(), o.stride(0),
+                                             gate.data_ptr(), gate.stride(0), weight.data_ptr(), _code(weight, "head_norm_gate weight"),
+                                             vdim if weight_per_head else 0, o.shape[0], heads, vdim, float(eps), float(scale),
+                                             _stream()), "head_norm_gate")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# several residual streams (csrc/hyper.cu)
+# ---------------------------------------------------------------------------
+def hyper_fanout(X: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """X[t, s, :] = h[t, :] for every stream s; X float32 [tokens, streams, width]."""
+    _cuda(X, h)
+    if X.dtype != torch.float32 or X.dim() != 3 or not (X.is_contiguous() and h.is_contiguous()) or h.shape != (X.shape[0], X.shape[2]):
+        raise KernelError(f"hyper_fanout: X={tuple(X.shape)} h={tuple(h.shape)}")
+    _lib.check(_lib.load().oi_hyper_fanout(X.data_ptr(), h.data_ptr(), _code(h, "hyper_fanout"), X.shape[0], X.shape[1], X.shape[2],
+                                           _stream()), "hyper_fanout")
+    return X
+
+
+def hyper_step(X: torch.Tensor, *, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+               b_out: Optional[torch.Tensor] = None, a_in: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+               eps: float = 0.0, weight_offset: float = 0.0, out: Optional[torch.Tensor] = None,
+               row_idx: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """With ``y`` (float32 [tokens, width]): X[t, r] <- sum_s mix[s, r] X[t, s] + b_out[r] y[t] (in place; no coefficients:
+    X + y). With ``out``: out[t] = rms(sum_s a_in[s] X[t, s]) * (weight_offset + norm_w) from the new streams; ``row_idx``
+    gathers the rows that are read (then nothing is written to X)."""
+    _cuda(X, y, mix, b_out, a_in, norm_w, out, row_idx)
+    _i32(row_idx, "hyper_step row_idx")
+    T, S, W = X.shape
+    if X.dtype != torch.float32 or not X.is_contiguous():
+        raise KernelError("hyper_step: the streams must be contiguous float32 [tokens, streams, width]")
+    if y is not None and (y.dtype != torch.float32 or y.shape != (T, W) or not y.is_contiguous()):
+        raise KernelError(f"hyper_step: y must be contiguous float32 [{T}, {W}], got {tuple(y.shape)} {y.dtype}")
+    coefs = [t for t in (mix, b_out, a_in) if t is not None]
+    for t, n in ((mix, S * S), (b_out, S), (a_in, S)):
+        if t is not None and (t.numel() != n or not t.is_contiguous() or t.dtype != coefs[0].dtype):
+            raise KernelError("hyper_step: the coefficients must be contiguous, of one type, [S, S], [S] and [S]")
+    rows = T if row_idx is None else row_idx.numel()
+    if out is not None and (out.shape != (rows, W) or not out.is_contiguous() or norm_w is None or norm_w.numel() != W):
+        raise KernelError("hyper_step: out must be contiguous [rows, width] and the norm weight [width]")
+    _lib.check(_lib.load().oi_hyper_step(
+        X.data_ptr(), rows, S, W, _ptr(y), 0, 1.0, 0.0, _ptr(mix), _ptr(b_out), _ptr(a_in), _code(coefs[0], "hyper_step") if coefs else 0,
+        _ptr(norm_w), 0 if norm_w is None else _code(norm_w, "hyper_step norm"), float(eps), float(weight_offset), _ptr(out),
+        0 if out is None else _code(out, "hyper_step out"), _ptr(row_idx), _stream()), "hyper_step")
+    return out
+
+
+def scaled_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ca: float, cb: float) -> torch.Tensor:
+    """out = ca * a + cb * b, float32."""
+    _cuda(out, a, b)
+    if not (out.dtype == a.dtype == b.dtype == torch.float32) or out.shape != a.shape or a.shape != b.shape \
+            or not (out.is_contiguous() and a.is_contiguous() and b.is_contiguous()):
+        raise KernelError("scaled_sum: three contiguous float32 tensors of one shape")
+    _lib.check(_lib.load().oi_scaled_sum(out.data_ptr(), a.data_ptr(), b.data_ptr(), float(ca), float(cb), out.numel(), _stream()),
+               "scaled_sum")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# routed experts (csrc/moe.cu)
+# ---------------------------------------------------------------------------
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int):
+    """Router logits in float32, the ``top`` largest per row and their softmax, and the rows grouped by expert.
+    Returns (ids [rows, top] int32, weights [rows, top] float32, sorted pairs, tile list): the last two feed ``moe_experts``."""
+    _cuda(x, w_router)
+    rows, K = x.shape
+    E = w_router.shape[0]
+    if x.stride(1) != 1 or not w_router.is_contiguous() or w_router.shape[1] != K:
+        raise KernelError(f"moe_route: x={tuple(x.shape)} router={tuple(w_router.shape)}")
+    L = _lib.load()
+    ids = torch.empty((rows, top), dtype=torch.int32, device=x.device)
+    wts = torch.empty((rows, top), dtype=torch.float32, device=x.device)
+    order = torch.empty(rows * top, dtype=torch.int32, device=x.device)
+    tiles = torch.empty(3 * L.oi_moe_max_tiles(rows * top, E) + 1, dtype=torch.int32, device=x.device)
+    _lib.check(L.oi_moe_route(x.data_ptr(), _code(x, "moe_route"), x.stride(0), w_router.data_ptr(), _code(w_router, "moe_route router"),
+                              rows, K, E, int(top), ids.data_ptr(), wts.data_ptr(), order.data_ptr(), tiles.data_ptr(), _stream()),
+               "moe_route")
+    return ids, wts, order, tiles
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, limit: float) -> torch.Tensor:
+    """sum_j weight_j * down_e(act(gate_e x, up_e x)) over a row's chosen experts; float32 [rows, width].
+    ``w_gate_up`` [E, 2 F, W] (F gate rows, then F up rows), ``w_down`` [E, W, F], in x's type."""
+    ids, wts, order, tiles = routing
+    _cuda(x, w_gate_up, w_down)
+    rows, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    top = ids.shape[1]
+    if w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype or w_down.shape != (E, W, F2 // 2) or x.stride(1) != 1 \
+            or not (w_gate_up.is_contiguous() and w_down.is_contiguous()):
+        raise KernelError("moe_experts: the experts' weights must be contiguous, in x's type, [E, 2F, W] and [E, W, F]")
+    act = torch.empty((rows * top, F2 // 2), dtype=x.dtype, device=x.device)
+    y = torch.empty((rows * top, W), dtype=torch.float32, device=x.device)
+    out = torch.empty((rows, W), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().oi_moe_experts(x.data_ptr(), _code(x, "moe_experts"), x.stride(0), w_gate_up.data_ptr(), w_down.data_ptr(), rows,
+                                          W, F2 // 2, E, top, float(limit), order.data_ptr(), tiles.data_ptr(), wts.data_ptr(),
+                                          act.data_ptr(), y.data_ptr(), out.data_ptr(), _stream()), "moe_experts")
+    return out

@@ -1,2 +1,2 @@
 """Built-in architectures. Importing this package registers them."""
-from . import delunex, qwen3  # noqa: F401
+from . import delunex, pilonex, qwen3  # noqa: F401

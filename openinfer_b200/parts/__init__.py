@@ -1,5 +1,5 @@
 """Parts a model is put together from, their specs and registries."""
-from . import attention, block, latent_attention, mlp, norm, position, stream  # noqa: F401  (register the built-in parts)
+from . import attention, block, latent_attention, mlp, moe, norm, parallel, position, recurrent, stream  # noqa: F401  (register the built-in parts)
 from .base import Block, CacheBinding, FeedForward, Mixer, Norm, Part, PositionEncoding
 from .registry import (
     build_block, build_feed_forward, build_mixer, build_norm, build_position_encoding,

@@ -132,3 +132,87 @@ class BranchNormBlock(Block):
         if low is not None:
             ctx.scratch["stream_low"] = low      # the stream as it goes on, rounded: what the next block's branch reads
         return h, None
+
+
+@dataclasses.dataclass
+class PendingBranch:
+    """A sublayer's result that has not reached the streams yet, with the coefficients it comes back by (None: added as
+    it is). The kernel that opens the next sublayer, or the final norm, carries it out."""
+
+    y: torch.Tensor
+    coefficients: Optional[Part] = None
+
+
+@register_block("hyper")
+class HyperBlock(Block):
+    """Pre-norm sublayers over ``streams`` residual streams X [tokens, S, hidden] in float32 (hyper-connections): a
+    sublayer reads u = sum_s a[s] x_s through its norm, and its result y comes back as x'_r = sum_s M[s, r] x_s + b[r] y,
+    every r from the old streams. With ``stream_coefficients`` off it is the plain pre-norm residual (a = b = 1, M = 1)
+    on a float32 stream. The feed-forward is optional. ONE kernel ends a sublayer and opens the next (csrc/hyper.cu),
+    across the border between two blocks too: the block hands its last result on as a ``PendingBranch``."""
+
+    stream_dtype = torch.float32
+    multi_stream = True
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__(spec)
+        self._mixer = build_mixer(spec.mixer)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.input_norm = build_norm(spec.input_norm)
+        self.post_norm = build_norm(spec.post_norm) if self.feed_forward is not None else None
+        for n in (self.input_norm, self.post_norm):
+            if n is not None and not isinstance(n, RmsNorm):
+                raise ValueError("a hyper block needs rms norms")
+        from .spec import StreamCoefficientsSpec
+        self.mixer_streams = self.ff_streams = None
+        if spec.stream_coefficients:
+            self.mixer_streams = build_stream_part(StreamCoefficientsSpec(streams=spec.streams))
+            if self.feed_forward is not None:
+                self.ff_streams = build_stream_part(StreamCoefficientsSpec(streams=spec.streams))
+        elif spec.streams != 1:
+            raise ValueError("several streams need their coefficients")
+        for part in (self._mixer, self.feed_forward):
+            if part is not None and not getattr(part, "takes_out_dtype", False):
+                raise ValueError(f"a hyper block needs parts that can return float32, {type(part).__name__} cannot")
+
+    @property
+    def mixer(self):
+        return self._mixer
+
+    def sub_parts(self) -> Dict[str, Part]:
+        s = self.spec
+        parts: Dict[str, Part] = {s.input_norm_name: self.input_norm, s.mixer_name: self._mixer}
+        if self.feed_forward is not None:
+            parts[s.post_norm_name] = self.post_norm
+            parts[s.feed_forward_name] = self.feed_forward
+        if self.mixer_streams is not None:
+            parts[s.mixer_streams_name] = self.mixer_streams
+        if self.ff_streams is not None:
+            parts[s.feed_forward_streams_name] = self.ff_streams
+        return parts
+
+    @staticmethod
+    def open_sublayer(X: torch.Tensor, pending: Optional[PendingBranch], reader: Optional[Part], norm: RmsNorm,
+                      dtype: torch.dtype) -> torch.Tensor:
+        """The pending result reaches the streams, and the next sublayer's input comes off them through its norm."""
+        out = torch.empty((X.shape[0], X.shape[2]), dtype=dtype, device=X.device)
+        c = pending.coefficients if pending is not None else None
+        ops.hyper_step(X, y=pending.y if pending is not None else None, mix=c.mix if c is not None else None,
+                       b_out=c.b_out if c is not None else None, a_in=reader.a_in if reader is not None else None,
+                       norm_w=norm.weight, eps=norm.spec.eps, weight_offset=norm.spec.weight_offset, out=out)
+        return out
+
+    def forward(self, h: torch.Tensor, pending, ctx, binding: CacheBinding):
+        if h.dim() != 3 or h.dtype != torch.float32 or h.shape[1] != self.spec.streams:
+            raise RuntimeError(f"a hyper block takes float32 streams [tokens, {self.spec.streams}, hidden]")
+        if pending is not None and not isinstance(pending, PendingBranch):
+            raise RuntimeError("a hyper block follows hyper blocks only")
+        dtype = ctx.scratch["model_dtype"]
+        x = self.open_sublayer(h, pending, self.mixer_streams, self.input_norm, dtype)
+        a = self._mixer.forward(x, ctx, binding, out_dtype=torch.float32)
+        pending = PendingBranch(a, self.mixer_streams)
+        if self.feed_forward is not None:
+            x = self.open_sublayer(h, pending, self.ff_streams, self.post_norm, dtype)
+            m = self.feed_forward.forward(x, ctx, out_dtype=torch.float32)
+            pending = PendingBranch(m, self.ff_streams)
+        return h, pending

@@ -13,7 +13,7 @@ import torch
 
 from ..kernels import gemm_tcgen05, native, ops
 from ..kernels import lib as _lib
-from ..kernels.linear import ensure_library
+from ..kernels.linear import ensure_library, linear
 from .base import FeedForward
 from .registry import register_feed_forward
 from .spec import GatedMlpSpec, ParamInfo
@@ -24,32 +24,36 @@ from .spec import GatedMlpSpec, ParamInfo
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec) -> None:
         super().__init__(spec)
-        self.act_code = ops.act_code(spec.activation)   # refuses a name no kernel knows; the kernels take the code
+        self.act_code = ops.glu_code(spec.activation)   # refuses a name no kernel knows; the kernels take the code
+        # activations with a limit are formed by the stand-alone kernel behind the plain gate|up product
+        self.fused = spec.activation in ops.ACTIVATIONS
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamInfo]:
         s = self.spec
         return {
-            "gate_proj.weight": ParamInfo((s.intermediate_size, s.hidden_size)),
-            "up_proj.weight": ParamInfo((s.intermediate_size, s.hidden_size)),
-            "down_proj.weight": ParamInfo((s.hidden_size, s.intermediate_size)),
+            s.gate_name: ParamInfo((s.intermediate_size, s.hidden_size)),
+            s.up_name: ParamInfo((s.intermediate_size, s.hidden_size)),
+            s.down_name: ParamInfo((s.hidden_size, s.intermediate_size)),
         }
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.spec.gate_name], tensors[self.spec.up_name]
         if g.dtype != u.dtype:
             raise ValueError("gate_proj and up_proj must be stored in one dtype to be fused")
         inter = self.spec.intermediate_size
         # Rows of the fused matrix: blocks of `block` gate rows followed by the up rows of the same
         # indices. With block = 64 a 128-row tile of the tensor-core products holds a gate block and
         # its up block side by side, and the activation is formed in those kernels' epilogues.
-        self.block = gemm_tcgen05.ACT_BLOCK if (g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
+        self.block = gemm_tcgen05.ACT_BLOCK if (self.fused and g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
         nb = inter // self.block
         self.w_gate_up = torch.stack([g.view(nb, self.block, -1), u.view(nb, self.block, -1)], dim=1).reshape(2 * inter, -1).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_down = tensors[self.spec.down_name].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    takes_out_dtype = True
+
+    def forward(self, x: torch.Tensor, ctx, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """One native call (``oi_gated_mlp``): it picks, by the step's rows, the product that forms the activation in
         its epilogue (tcgen05 tiles from 128 rows, the weight stream up to 32) or the plain product and the
         stand-alone activation kernel, then the down projection."""
@@ -61,6 +65,10 @@ class GatedMlp(FeedForward):
             x = x.contiguous()
         if M > 32:
             ensure_library(x.device)
+        if not self.fused or out_dtype not in (None, x.dtype):
+            gate_up = linear(x, self.w_gate_up)
+            act = ops.glu_act(torch.empty((M, inter), dtype=x.dtype, device=x.device), gate_up, self.block, s.activation, s.limit)
+            return linear(act, self.w_down, out_dtype=out_dtype)
         out = torch.empty((M, s.hidden_size), dtype=x.dtype, device=x.device)
         act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         gate_up = None

@@ -138,6 +138,9 @@ class Model:
             self.bindings.append(CacheBinding(kv=kv, owns_kv=owns, states=states))
 
     # ------------------------------------------------------------------ forward
+    def multi_stream(self) -> bool:
+        return any(getattr(b, "multi_stream", False) for b in self.blocks)
+
     def stream_dtype(self) -> torch.dtype:
         return torch.float32 if self.spec.residual_dtype == "float32" else self.dtype
 
@@ -150,6 +153,15 @@ class Model:
             ops.scale_cap(h, scale=self.spec.embedding_scale)
         ctx.scratch["model_dtype"] = self.dtype
         ctx.scratch.pop("stream_low", None)
+        if self.multi_stream():
+            # several residual streams, all equal to the embedding output at the start
+            S = self.spec.streams
+            if S > 1:
+                X = torch.empty((ctx.num_tokens, S, self.spec.hidden_size), dtype=torch.float32, device=self.device)
+                ops.hyper_fanout(X, h)
+                h = X
+            else:
+                h = h.view(ctx.num_tokens, 1, self.spec.hidden_size)
         if any(self.blocks[c.layer].wants_history for c in self.calls):
             # the embedding output and every block's result, for blocks that average over them
             history = torch.empty((len(self.calls) + 1, ctx.num_tokens, self.spec.hidden_size), dtype=h.dtype, device=self.device)
@@ -227,7 +239,7 @@ class Model:
             a.cos_tab, a.sin_tab = (0, 0) if cos is None else (cos.data_ptr(), sin.data_ptr())
             a.rot_half, a.max_pos = (0, 0) if cos is None else (cos.shape[1], cos.shape[0])
             a.nq, a.nkv, a.hd, a.window = s.num_heads, s.num_kv_heads, s.head_dim, int(s.window) if s.window else 0
-            a.scale, a.eps, a.w_offset = s.softmax_scale, (qn.eps if qn else 0.0), (qn.weight_offset if qn else 0.0)
+            a.scale, a.eps, a.w_offset = at.scale, (qn.eps * at.norm_eps_factor if qn else 0.0), (qn.weight_offset if qn else 0.0)
             a.write_kv, a.rope_mode = (1 if binding.owns_kv else 0), 1
             a.interleaved = 1 if getattr(s.position, "interleaved", False) else 0
         sp = self.spec
@@ -418,7 +430,15 @@ class Model:
     def logits(self, h: torch.Tensor, pending: Optional[torch.Tensor], row_idx: torch.Tensor) -> torch.Tensor:
         """Float32 logits [rows, vocab] of the wanted rows only: gather + final norm in one
         kernel, then the head (pegainfer-qwen3/src/prefill.rs:440-477)."""
-        if h.dtype != self.dtype:
+        if h.dim() == 3:
+            # several streams: the last sublayer's result reaches them, then the wanted rows' streams are summed and normed
+            if pending is not None:
+                c = pending.coefficients
+                ops.hyper_step(h, y=pending.y, mix=c.mix if c is not None else None, b_out=c.b_out if c is not None else None)
+            n = self.final_norm
+            x = torch.empty((row_idx.numel(), h.shape[2]), dtype=self.dtype, device=h.device)
+            ops.hyper_step(h, norm_w=n.weight, eps=n.spec.eps, weight_offset=n.spec.weight_offset, out=x, row_idx=row_idx)
+        elif h.dtype != self.dtype:
             x = self.final_norm(h, delta=pending, row_idx=row_idx, out_dtype=self.dtype)
         else:
             x = self.final_norm(h, delta=pending, row_idx=row_idx)

@@ -1,0 +1,65 @@
+"""Routed experts: ``experts`` small gated feed-forwards of which every row uses ``top``.
+
+Router logits z = W_r x are formed in float32; the ``top`` largest choose (ties to the lower index) and the softmax over
+the chosen logits alone weighs the experts' outputs. Each expert is down(act(gate x, up x)) with the spec's gated
+activation. The experts' matrices are stacked when they are loaded ([experts, 2 ff, hidden] and [experts, hidden, ff]); a
+step routes, groups its (row, choice) pairs by expert on the device, runs the two grouped products and sums a row's
+choices in a fixed order (csrc/moe.cu). Nothing of a step's routing is read on the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward
+from .registry import register_feed_forward
+from .spec import ParamInfo, RoutedExpertsSpec
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    takes_out_dtype = True
+
+    def __init__(self, spec: RoutedExpertsSpec) -> None:
+        super().__init__(spec)
+        s = spec
+        if not 0 < s.top <= s.experts or s.top > 32 or s.intermediate_size <= 0:
+            raise ValueError(f"routed_experts: {s.top} of {s.experts} experts (at most 32 a row), ff {s.intermediate_size}")
+        if s.activation != "swiglu_clamp":
+            raise ops.KernelError(f"routed_experts: activation {s.activation!r} has no kernel (known: swiglu_clamp)")
+        self.w_router: Optional[torch.Tensor] = None
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def _names(self, e: int):
+        s = self.spec
+        p = f"{s.expert_prefix}{e}."
+        return p + s.gate_name, p + s.up_name, p + s.down_name
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s = self.spec
+        W, F = s.hidden_size, s.intermediate_size
+        p = {s.router_name: ParamInfo((s.experts, W), ("normal", W ** -0.5))}
+        for e in range(s.experts):
+            g, u, d = self._names(e)
+            p[g] = ParamInfo((F, W), ("normal", W ** -0.5))
+            p[u] = ParamInfo((F, W), ("normal", W ** -0.5))
+            p[d] = ParamInfo((W, F), ("normal", F ** -0.5))
+        return p
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.w_router = tensors[s.router_name].contiguous()
+        names = [self._names(e) for e in range(s.experts)]
+        self.w_gate_up = torch.stack([torch.cat([tensors[g], tensors[u]], dim=0) for g, u, _ in names]).contiguous()
+        self.w_down = torch.stack([tensors[d] for _, _, d in names]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        s = self.spec
+        if not x.is_contiguous():
+            x = x.contiguous()
+        routing = ops.moe_route(x, self.w_router, s.top)
+        out = ops.moe_experts(x, self.w_gate_up, self.w_down, routing, s.limit)
+        return out if out_dtype in (None, torch.float32) else out.to(out_dtype)

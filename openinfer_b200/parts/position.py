@@ -13,6 +13,7 @@ bfloat16; here it stays float32.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -36,14 +37,27 @@ class RotaryEncoding(PositionEncoding):
 
     def rotation_tables(self, device: torch.device):
         s = self.spec
-        key = (s.rotary_dim, float(s.theta), s.max_positions, str(device))
+        key = (s.rotary_dim, float(s.theta), s.max_positions, s.scaling, str(device))
         if key not in _TABLES:
             half = s.rotary_dim // 2
-            idx = torch.arange(half, dtype=torch.float32)
-            inv_freq = 1.0 / torch.pow(torch.tensor(float(s.theta), dtype=torch.float32),
-                                       idx * 2.0 / s.rotary_dim)
-            ang = torch.arange(s.max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
-            _TABLES[key] = (torch.cos(ang).contiguous().to(device), torch.sin(ang).contiguous().to(device))
+            if s.scaling is None:
+                idx = torch.arange(half, dtype=torch.float32)
+                inv_freq = 1.0 / torch.pow(torch.tensor(float(s.theta), dtype=torch.float32),
+                                           idx * 2.0 / s.rotary_dim)
+                ang = torch.arange(s.max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
+            else:
+                # stretched long waves: the frequencies are formed in float64 and rounded once to float32; the angle is
+                # the exact product of the position and that float32 frequency
+                factor, low, high, original = (float(v) for v in s.scaling)
+                idx = torch.arange(half, dtype=torch.float64)
+                f = float(s.theta) ** (-2.0 * idx / s.rotary_dim)
+                wave = 2.0 * math.pi / f
+                t = (original / wave - low) / (high - low)
+                f = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, (1.0 - t) * f / factor + t * f))
+                f = f.to(torch.float32).to(torch.float64)
+                ang = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * f[None, :]
+            _TABLES[key] = (torch.cos(ang).to(torch.float32).contiguous().to(device),
+                            torch.sin(ang).to(torch.float32).contiguous().to(device))
         return _TABLES[key]
 
 

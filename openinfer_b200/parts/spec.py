@@ -24,6 +24,7 @@ class ParamInfo:
     shape: Tuple[int, ...]
     init: Tuple = ("normal", 0.02)
     integer: bool = False
+    free_dims: Tuple[int, ...] = ()   # dimensions whose size the checkpoint decides (``shape`` there: what random weights use)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -44,6 +45,10 @@ class PositionSpec:
     theta: float = 10000.0
     max_positions: int = 0
     interleaved: bool = False   # angle d turns the neighbours (2 d, 2 d + 1) instead of (d, d + rotary_dim / 2)
+    # long waves stretched, (factor, low, high, original): a frequency f with wavelength l = 2 pi / f stays for
+    # l < original / high, becomes f / factor for l > original / low, and in between (1 - s) f / factor + s f with
+    # s = (original / l - low) / (high - low)
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -57,6 +62,16 @@ class AttentionSpec:
     position: PositionSpec = PositionSpec(kind="none")
     qk_norm: Optional[NormSpec] = None      # per-head norm over head_dim, before the rotation
     window: Optional[int] = None            # keys visible to a query, itself included; None = all
+    # queries / keys and values of other sizes than head_dim (None: head_dim). head_dim is then the cached row, a multiple
+    # of 8 that holds both; the projections are padded with zero rows at load time and the norm's constants follow
+    qk_dim: Optional[int] = None
+    v_dim: Optional[int] = None
+    q_name: str = "q_proj.weight"
+    k_name: str = "k_proj.weight"
+    v_name: str = "v_proj.weight"
+    o_name: str = "o_proj.weight"
+    q_norm_name: str = "q_norm.weight"
+    k_norm_name: str = "k_norm.weight"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -122,11 +137,91 @@ class DepthAverageSpec:
 
 
 @dataclasses.dataclass(frozen=True)
+class StreamCoefficientsSpec:
+    """How one sublayer reads S residual streams and writes back to them (three small tensors)."""
+
+    kind: str = "stream_coefficients"
+    streams: int = 1
+    in_name: str = "in"
+    mix_name: str = "mix"
+    out_name: str = "out"
+
+
+@dataclasses.dataclass(frozen=True)
 class GatedMlpSpec:
     kind: str = "gated_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    limit: float = 0.0                      # of activations that clamp ("swiglu_clamp")
+    gate_name: str = "gate_proj.weight"
+    up_name: str = "up_proj.weight"
+    down_name: str = "down_proj.weight"
+
+
+@dataclasses.dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """``experts`` gated feed-forwards of which every row uses the ``top`` with the largest router logits, weighted by
+    the softmax over those logits. Tensors: ``router_name`` [experts, hidden] and per expert ``expert_prefix`` + index +
+    "." + gate / up / down names."""
+
+    kind: str = "routed_experts"
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    experts: int = 0
+    top: int = 0
+    activation: str = "swiglu_clamp"
+    limit: float = 0.0
+    router_name: str = "router"
+    expert_prefix: str = "e"
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+
+
+@dataclasses.dataclass(frozen=True)
+class MatrixMemorySpec:
+    """A recurrent mixer with a matrix C [qk_dim, v_dim], a normaliser n and a running maximum m per head (the mLSTM cell):
+    exponential input gate and sigmoid forget gate in the log domain, both soft-capped at ``gate_cap``."""
+
+    kind: str = "matrix_memory"
+    hidden_size: int = 0
+    num_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    gate_cap: float = 0.0
+    eps: float = 1e-6                       # of the per-head unit norm of the read-out
+
+
+@dataclasses.dataclass(frozen=True)
+class GatedDeltaSpec:
+    """A recurrent mixer with a matrix C [qk_dim, v_dim] per head updated by the delta rule, one decay per head and key
+    channel; queries, keys and values pass a short causal filter over time and silu first. The decay and the output
+    gate come through low-rank products whose inner sizes the checkpoint decides."""
+
+    kind: str = "gated_delta"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    conv_taps: int = 0
+    eps: float = 1e-6
+    decay_rank: int = 0                     # what random weights use; a checkpoint's own sizes win
+    gate_rank: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input; the result is left_scale * left + right_scale * right."""
+
+    kind: str = "parallel"
+    left: Any = None
+    right: Any = None
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    left_name: str = "left."
+    right_name: str = "right."
 
 
 @dataclasses.dataclass(frozen=True)
@@ -147,6 +242,12 @@ class BlockSpec:
     input_conv_name: str = "conv."
     depth_average: Any = None                    # blocks whose result is averaged with earlier layers' (DepthAverageSpec)
     depth_average_name: str = "depth."
+    # blocks over several residual streams ("hyper"): how many, whether the layer has the three coefficient tensors per
+    # sublayer, and their names
+    streams: int = 1
+    stream_coefficients: bool = False
+    mixer_streams_name: str = "hc1."
+    feed_forward_streams_name: str = "hc2."
 
 
 @dataclasses.dataclass(frozen=True)
@@ -177,6 +278,7 @@ class ModelSpec:
     logit_soft_cap: float = 0.0      # > 0: logits = cap * tanh(logits / cap)
     logit_scale: float = 1.0         # the logits are multiplied by this
     residual_dtype: str = "model"    # "model": the stream between layers has the model's type; "float32": always 32-bit
+    streams: int = 1                 # residual streams a row travels as ([tokens, streams, hidden]; blocks of kind "hyper")
 
     def calls(self) -> List[LayerCall]:
         return [c if isinstance(c, LayerCall) else LayerCall(int(c)) for c in self.order]

@@ -18,7 +18,7 @@ from ..cache.manager import StateNeed
 from ..kernels import ops
 from .base import Part
 from .registry import register_stream_part
-from .spec import DepthAverageSpec, ParamInfo, ShortConvSpec
+from .spec import DepthAverageSpec, ParamInfo, ShortConvSpec, StreamCoefficientsSpec
 
 
 @register_stream_part("short_conv")
@@ -64,3 +64,29 @@ class DepthAverage(Part):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.spec.param_name].contiguous()
+
+
+@register_stream_part("stream_coefficients")
+class StreamCoefficients(Part):
+    """The three small tensors of one sublayer over S residual streams: ``in`` [S] (how the sublayer's input is read off
+    the streams), ``mix`` [S, S] (indexed [from, to]: how the streams are carried over) and ``out`` [S] (how the sublayer's
+    result is added to each). It owns the tensors only; ``ops.hyper_step`` applies them."""
+
+    def __init__(self, spec: StreamCoefficientsSpec) -> None:
+        super().__init__(spec)
+        if not 1 <= spec.streams <= 8:
+            raise ValueError(f"stream_coefficients: {spec.streams} streams, 1 to 8 are supported")
+        self.a_in: Optional[torch.Tensor] = None
+        self.mix: Optional[torch.Tensor] = None
+        self.b_out: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s, n = self.spec, self.spec.streams
+        return {s.in_name: ParamInfo((n,), ("normal_around", 0.2, 1.0 / n)), s.out_name: ParamInfo((n,), ("normal_around", 0.3, 1.0)),
+                s.mix_name: ParamInfo((n, n), ("eye_plus_normal", 0.2))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.a_in = tensors[s.in_name].contiguous()
+        self.b_out = tensors[s.out_name].to(self.a_in.dtype).contiguous()
+        self.mix = tensors[s.mix_name].to(self.a_in.dtype).contiguous()

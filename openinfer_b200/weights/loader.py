@@ -101,7 +101,8 @@ def load_tensors(folder: str, expected: Dict[str, ParamInfo], model_dtype: torch
         if name not in index:
             continue
         _, shape, stored = index[name]
-        if tuple(shape) != tuple(info.shape):
+        free = getattr(info, "free_dims", ())
+        if len(shape) != len(info.shape) or any(a != b for i, (a, b) in enumerate(zip(shape, info.shape)) if i not in free):
             wrong_shape.append(f"{name}: has shape {list(shape)}, the config expects {list(info.shape)}")
         if _target_dtype(stored, info.integer, model_dtype) is None:
             kind = "an integer" if info.integer else "a floating"

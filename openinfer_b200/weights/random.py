@@ -41,6 +41,8 @@ def random_tensors(expected: Dict[str, ParamInfo], seed: int, dtype: torch.dtype
             t = t + 1.0
         elif kind == "normal_around":      # ("normal_around", std, mean)
             t = t + float(info.init[2])
+        elif kind == "eye_plus_normal":    # a square matrix around the identity
+            t = t + torch.eye(info.shape[0], device=device, dtype=torch.float32)
         elif kind != "normal":
             raise ValueError(f"{name}: unknown init {kind!r}")
         out[name] = t.to(dtype)
