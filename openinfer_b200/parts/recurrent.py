@@ -59,8 +59,10 @@ class MatrixMemory(Mixer):
         return {"q": ParamInfo((H * D, W), ("normal", std)), "k": ParamInfo((H * D, W), ("normal", std)),
                 "v": ParamInfo((H * V, W), ("normal", std)), "g": ParamInfo((H * V, W), ("normal", std)),
                 "o": ParamInfo((W, H * V), ("normal", (H * V) ** -0.5)), "norm": ParamInfo((H * V,), ("one_plus_normal", 0.1)),
-                "i": ParamInfo((H, W), ("normal", std)), "i.b": ParamInfo((H,), ("normal", 1.0)),
-                "f": ParamInfo((H, W), ("normal", std)), "f.b": ParamInfo((H,), ("normal_around", 1.0, 2.0))}
+                # random weights: a mild input gate around 0 and a forget gate near one keep the running maximum small, so
+                # that both sides of the read-out's max(|n . q|, e^-m) occur and a rounding is not amplified by a tiny divisor
+                "i": ParamInfo((H, W), ("normal", 0.3 * std)), "i.b": ParamInfo((H,), ("normal", 0.3)),
+                "f": ParamInfo((H, W), ("normal", std)), "f.b": ParamInfo((H,), ("normal_around", 0.5, 4.0))}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         rows = [tensors[n] for n in ("q", "k", "v", "g", "i", "f")]

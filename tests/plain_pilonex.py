@@ -64,9 +64,14 @@ def clamped_glu(x: torch.Tensor, w_gate, w_up, w_down, limit: float) -> torch.Te
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w_down.T
 
 
-def routed_experts(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, experts: int, top: int, limit: float) -> torch.Tensor:
+def routed_experts(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, experts: int, top: int, limit: float,
+                   margins: Optional[list] = None) -> torch.Tensor:
+    """``margins``: receives, per row, how far the last chosen logit lies above the first one left out."""
     z = x @ W[pre + "router"].T                         # [T, experts]
     out = torch.zeros_like(x)
+    if margins is not None:
+        ranked = torch.sort(z, dim=1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < experts else torch.full((x.shape[0],), float("inf"), dtype=x.dtype))
     for t in range(x.shape[0]):
         order = sorted(range(experts), key=lambda e: (-float(z[t, e]), e))[:top]
         zs = torch.stack([z[t, e] for e in order])
@@ -77,11 +82,11 @@ def routed_experts(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, expert
     return out
 
 
-def feed_forward(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, mlp: dict) -> torch.Tensor:
+def feed_forward(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, mlp: dict, margins: Optional[list] = None) -> torch.Tensor:
     if mlp["kind"] == "dense":
         return clamped_glu(x, W[pre + "gate"], W[pre + "up"], W[pre + "down"], float(mlp["limit"]))
     if mlp["kind"] == "moe":
-        return routed_experts(x, W, pre, int(mlp["router"]["experts"]), int(mlp["router"]["top"]), float(mlp["expert"]["limit"]))
+        return routed_experts(x, W, pre, int(mlp["router"]["experts"]), int(mlp["router"]["top"]), float(mlp["expert"]["limit"]), margins)
     raise ValueError(mlp["kind"])
 
 
@@ -208,26 +213,33 @@ def mixer(x: torch.Tensor, W: Dict[str, torch.Tensor], pre: str, layer: dict, ep
 
 # ----------------------------------------------------------------------------- the model
 def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence. ``layers_out``: receives the stream after every layer run."""
+            layers_out: Optional[list] = None, router_margins: Optional[list] = None, round_to=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence. ``layers_out``: receives the stream after every layer run;
+    ``router_margins``: per routed feed-forward that ran, every row's margin between chosen and left-out experts;
+    ``round_to``: every sublayer's normed input is rounded to this type (what an engine that hands 16-bit rows to its
+    products does at the least), to see how far such roundings alone move the logits of a model."""
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     S = cfg.get("streams")
+
+    def rounded(v):
+        return v if round_to is None else v.to(round_to).to(dtype)
+
     x0 = W["embed"][torch.tensor(tokens, dtype=torch.long)]
     X = [x0.clone() for _ in range(int(S))] if S else [x0]
     for i in run_order(cfg):
         layer, pre = cfg["layers"][i], f"l{i}."
         subs = [(1, lambda u: mixer(u, W, pre + "mix.", layer, eps))]
         if layer.get("mlp"):
-            subs.append((2, lambda u: feed_forward(u, W, pre + "mlp.", layer["mlp"])))
+            subs.append((2, lambda u: feed_forward(u, W, pre + "mlp.", layer["mlp"], router_margins)))
         for qn, f in subs:
             if S:
                 a, M, b = W[f"{pre}hc{qn}.in"], W[f"{pre}hc{qn}.mix"], W[f"{pre}hc{qn}.out"]
                 u = sum(a[s] * X[s] for s in range(len(X)))
-                y = f(rms_one_plus(u, W[f"{pre}norm{qn}"], eps))
+                y = f(rounded(rms_one_plus(u, W[f"{pre}norm{qn}"], eps)))
                 X = [sum(M[s, r] * X[s] for s in range(len(X))) + b[r] * y for r in range(len(X))]
             else:
-                X = [X[0] + f(rms_one_plus(X[0], W[f"{pre}norm{qn}"], eps))]
+                X = [X[0] + f(rounded(rms_one_plus(X[0], W[f"{pre}norm{qn}"], eps)))]
         if layers_out is not None:
             layers_out.append(sum(X))
-    return rms_one_plus(sum(X), W["final.norm"], eps) @ W["head"].T
+    return rounded(rms_one_plus(sum(X), W["final.norm"], eps)) @ W["head"].T
