@@ -20,7 +20,8 @@ exits with 2.
 
 ``--design delunex`` measures something else and leaves the above as it is: the Delunex design at layer sizes of
 real models beside Qwen3 at equal sizes (decode at batch 1 / 8 / 64, a 2,048-token prefill, with ``--design-kernels``
-every kernel's time per step), one JSON line of its own.
+every kernel's time per step), one JSON line of its own. ``--design pilonex`` does the same for the Pilonex design
+(hyper-connection streams, windowed attention beside a gated delta rule, matrix memories, dense and routed feed-forwards).
 """
 from __future__ import annotations
 
@@ -436,6 +437,51 @@ def design_configs(key, layers=None):
     return delunex, qwen
 
 
+def pilonex_configs(key, layers=None):
+    """Pilonex at the same widths and depths: of every four layers three are "parallel" (windowed grouped-query attention
+    with per head 128 keys and values, a quarter as many kv heads, rotary positions with stretched long waves, beside a
+    gated delta rule of half as many heads behind four-tap filters) and one is a matrix memory; the feed-forwards
+    alternate between a dense gated layer of Qwen3's size and sixteen experts of a third of it of which a token uses two;
+    two residual streams. Qwen3 as in ``design_configs``."""
+    width, n_layers, heads, window, _, inter = DESIGN_SIZES[key]
+    n_layers = layers or n_layers
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window},
+            "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": max(1, heads // 2), "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+             "gate_rank": 64}
+    lay = []
+    for i in range(n_layers):
+        mlp = ({"kind": "dense", "ff": inter, "limit": 7.0} if i % 2 == 0 else
+               {"kind": "moe", "expert": {"ff": inter // 4, "limit": 7.0}, "router": {"experts": 16, "top": 2}})
+        if i % 4 == 2:
+            lay.append({"type": "mlstm", "mixer": {"heads": max(1, heads // 2), "dim": 128, "vdim": 256, "gate_cap": 15.0}, "mlp": mlp})
+        else:
+            lay.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp})
+    pilonex = {"architecture": "Pilonex", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "streams": 2, "layers": lay}
+    return pilonex, design_configs(key, layers)[1]
+
+
+def _part_tensors(torch, part, seen=None):
+    """Every tensor a part holds, the tensors of parts inside it included."""
+    seen = set() if seen is None else seen
+    out = []
+    for v in vars(part).values():
+        if isinstance(v, torch.Tensor):
+            if v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                out.append(v)
+        elif hasattr(v, "parameters") and hasattr(v, "spec") and id(v) not in seen:
+            seen.add(id(v))
+            out += _part_tensors(torch, v, seen)
+    return out
+
+
+def _attention_specs(mixer):
+    """(heads, cached row, window) of every paged attention inside a mixer."""
+    sides = [mixer.left, mixer.right] if hasattr(mixer, "left") else [mixer]
+    return [(m.spec.num_heads, m.kv_need().head_dim, m.kv_need().window) for m in sides if m.kv_need() is not None]
+
+
 class DesignBench:
     """One model (any registered architecture) on the GPU with requests whose contexts are filled, not computed."""
 
@@ -449,6 +495,8 @@ class DesignBench:
         self.runner.cuda_graph = True
         for g in self.runner.cache.groups:
             g.tensor.normal_(0.0, 0.5)
+        for t in self.runner.cache.state_tensors:       # recurrent memories as a long context leaves them: small, not zero
+            t.normal_(0.0, 0.05)
         self.rng = random.Random(0)
         self.vocab = self.runner.spec.vocab_size
         self.esize = 2 if dtype == "bfloat16" else 4
@@ -516,11 +564,25 @@ class DesignBench:
 
     # what the step has to move and to compute, from the assembled model itself
     def decode_bytes(self, batch):
-        total = self.runner.model.weight_bytes()
-        for call, binding in zip(self.runner.model.calls, self.runner.model.bindings):
-            need = self.runner.model.blocks[call.layer].mixer.kv_need()
-            keys = min(self.context, need.window) if need.window else self.context
-            total += batch * keys * need.planes * need.num_kv_heads * need.head_dim * self.esize
+        model = self.runner.model
+        total = 0
+        seen = set()
+        for block in model.blocks:                      # every weight once; of routed experts only what `batch` rows can touch
+            for part in block.sub_parts().values():
+                for t in _part_tensors(self.torch, part, seen):
+                    share = 1.0
+                    if t.dim() == 3 and hasattr(part, "spec") and getattr(part.spec, "experts", 0):
+                        share = min(1.0, batch * part.spec.top / part.spec.experts)
+                    total += int(t.numel() * t.element_size() * share)
+        total += model.head.numel() * model.head.element_size()
+        for call, binding in zip(model.calls, model.bindings):
+            need = model.blocks[call.layer].mixer.kv_need()
+            if need is not None:
+                keys = min(self.context, need.window) if need.window else self.context
+                total += batch * keys * need.planes * need.num_kv_heads * need.head_dim * self.esize
+            for sid in binding.states:                  # recurrent state: one copy read, the other written
+                t = self.runner.cache.state_tensor(sid)
+                total += batch * t[0].numel() * t.element_size()
         return total
 
     def prefill_flops(self, T):
@@ -529,14 +591,18 @@ class DesignBench:
         for call in model.calls:
             block = model.blocks[call.layer]
             for part in block.sub_parts().values():
-                for v in vars(part).values():
-                    if isinstance(v, self.torch.Tensor) and v.dim() == 2 and v.shape[0] > 2 and v.shape[1] > 8:
+                for v in _part_tensors(self.torch, part):
+                    if v.dim() == 2 and v.shape[0] > 2 and v.shape[1] > 8:
                         flops += 2.0 * T * v.shape[0] * v.shape[1]
-            need = block.mixer.kv_need()
-            spec = block.mixer.spec
-            heads = spec.num_heads
-            seen = sum(min(t + 1, need.window) if need.window else t + 1 for t in range(T))
-            flops += 4.0 * heads * need.head_dim * seen
+                    elif v.dim() == 3 and getattr(part.spec, "experts", 0):      # routed experts: `top` of them a row
+                        flops += 2.0 * T * part.spec.top * v.shape[1] * v.shape[2]
+            for heads, row, window in _attention_specs(block.mixer):
+                seen = sum(min(t + 1, window) if window else t + 1 for t in range(T))
+                flops += 4.0 * heads * row * seen
+            for m in (block.mixer, getattr(block.mixer, "left", None), getattr(block.mixer, "right", None)):
+                sp = getattr(m, "spec", None)
+                if sp is not None and getattr(sp, "kind", "") in ("matrix_memory", "gated_delta"):   # memory update and read-out
+                    flops += 6.0 * T * sp.num_heads * sp.qk_dim * sp.v_dim
         return flops + 2.0 * self.vocab * model.spec.hidden_size
 
 
@@ -571,7 +637,8 @@ def design_mode(args, torch, mods, peaks, peaks_src):
             if key not in DESIGN_SIZES:
                 raise SystemExit(f"--design-sizes: unknown size {key!r} (known: {', '.join(DESIGN_SIZES)})")
             rec = {"width": DESIGN_SIZES[key][0], "layers": args.layers or DESIGN_SIZES[key][1]}
-            for arch, cfg in zip((args.design, "qwen3"), design_configs(key, args.layers)):
+            configs = pilonex_configs(key, args.layers) if args.design == "pilonex" else design_configs(key, args.layers)
+            for arch, cfg in zip((args.design, "qwen3"), configs):
                 b = DesignBench(torch, mods, cfg, args.dtype, CONTEXT, 64, steps + warm + 16)
                 r = {"weights_gb": round(b.runner.model.weight_bytes() / 1e9, 3)}
                 for batch in (1, 8, 64):
@@ -631,7 +698,7 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
-    ap.add_argument("--design", default=None, choices=["delunex"],
+    ap.add_argument("--design", default=None, choices=["delunex", "pilonex"],
                     help="instead of the headline workload: this design at layer sizes of real models beside Qwen3 at equal "
                          "sizes (decode at batch 1/8/64, a 2,048-token prefill), one JSON line")
     ap.add_argument("--design-sizes", default=None, help="sizes for --design, comma separated (1k, 2k, 4k; default 1k,2k)")

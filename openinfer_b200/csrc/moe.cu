@@ -15,7 +15,7 @@
 
 namespace {
 
-constexpr int kTileM = 32, kTileN = 64, kTileK = 16;
+constexpr int kTileM = 32, kTileN = 64, kTileK = 32;
 constexpr int kMaxTop = 32;
 
 template <typename T>
@@ -169,17 +169,47 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
   const T* We = Wt + (size_t)e * w_expert_stride;
   const int tn = threadIdx.x % 16, tm = threadIdx.x / 16;   // thread: rows tm, tm + 16; columns tn + 16 j, j < 4
   float acc[2][4] = {}, accu[2][4] = {};
+  // operands that can be read 16 bytes at a time (rows that start on 16-byte boundaries, K a multiple of the vector)
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const bool vec = K % kVec == 0 && lda % kVec == 0 && ((uintptr_t)A % 16 == 0) && ((uintptr_t)We % 16 == 0) &&
+                   ((size_t)N * K) % kVec == 0;
   for (int k0 = 0; k0 < K; k0 += kTileK) {
-    for (int i = threadIdx.x; i < kTileM * kTileK; i += 256) {
-      const int m = i / kTileK, k = i % kTileK;
-      const int r = src[m];
-      As[k][m] = (r >= 0 && k0 + k < K) ? to_f32(A[(size_t)r * lda + k0 + k]) : 0.f;
-    }
-    for (int i = threadIdx.x; i < kTileN * kTileK; i += 256) {
-      const int n = i / kTileK, k = i % kTileK;
-      const bool ok = n0 + n < N && k0 + k < K;
-      Wg[k][n] = ok ? to_f32(We[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
-      if (kGlu) Wu[k][n] = ok ? to_f32(We[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+    if (vec) {
+      constexpr int kChunks = kTileK / kVec;     // 16-byte pieces of a tile's row
+      for (int i = threadIdx.x; i < kTileM * kChunks; i += 256) {
+        const int m = i / kChunks, k = (i % kChunks) * kVec;
+        const int r = src[m];
+        T v[kVec] = {};
+        if (r >= 0 && k0 + k < K) *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(A + (size_t)r * lda + k0 + k);
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) As[k + e][m] = (r >= 0 && k0 + k < K) ? to_f32(v[e]) : 0.f;
+      }
+      for (int i = threadIdx.x; i < kTileN * kChunks; i += 256) {
+        const int n = i / kChunks, k = (i % kChunks) * kVec;
+        const bool ok = n0 + n < N && k0 + k < K;
+        T v[kVec] = {}, u[kVec] = {};
+        if (ok) {
+          *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(We + (size_t)(n0 + n) * K + k0 + k);
+          if (kGlu) *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(We + (size_t)(N + n0 + n) * K + k0 + k);
+        }
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          Wg[k + e][n] = ok ? to_f32(v[e]) : 0.f;
+          if (kGlu) Wu[k + e][n] = ok ? to_f32(u[e]) : 0.f;
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < kTileM * kTileK; i += 256) {
+        const int m = i / kTileK, k = i % kTileK;
+        const int r = src[m];
+        As[k][m] = (r >= 0 && k0 + k < K) ? to_f32(A[(size_t)r * lda + k0 + k]) : 0.f;
+      }
+      for (int i = threadIdx.x; i < kTileN * kTileK; i += 256) {
+        const int n = i / kTileK, k = i % kTileK;
+        const bool ok = n0 + n < N && k0 + k < K;
+        Wg[k][n] = ok ? to_f32(We[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+        if (kGlu) Wu[k][n] = ok ? to_f32(We[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll

@@ -9,18 +9,20 @@
 //                                    unit vectors (1e-6 inside the root), q times q_scale, beta = sigmoid(zb) and one decay
 //                                    per key channel g = exp(-exp(A_h) softplus(a + dt))
 //
-// One launch serves prompts and single decoded tokens alike: block (request, head, slice of 8 value columns) walks the
-// request's rows of the step in order, the state in registers (a column's D numbers spread over 16 lanes), the next row's
-// inputs requested while the current one is worked on. The state lives in two copies that take turns ([slots][2][heads]
-// [elems], C stored column by column, then n and m): a step reads copy state_phase[request] and leaves the other, so no
-// block reads what another writes. Everything is float32: the inputs are the float32 sums of the projections.
+// Prompts and single decoded tokens take the same two launches. A first kernel forms, for all rows at once, what does
+// not depend on earlier rows (gates, decays, unit vectors); then block (request, head, slice of value columns) walks the
+// request's rows of the step in order, its slice of C in registers (a column's D numbers spread over 4 to 16 lanes), the
+// rows' records staged in shared memory a chunk at a time (cp.async, two buffers), so that the loop over rows is the recurrence alone. The state
+// lives in two copies that take turns ([slots][2][heads][elems], C stored column by column, then n and m): a step reads
+// copy state_phase[request] and leaves the other, so no block reads what another writes. Everything is float32: the
+// inputs are the float32 sums of the projections.
 #include "common.cuh"
 
 namespace {
 
-constexpr int kLanes = 16;     // lanes that share a value column
-constexpr int kCols = 8;       // value columns per block
 enum : int { kMatrixMemory = 0, kGatedDelta = 1 };
+constexpr int kThreads = 128;
+constexpr int kMaxRegs = 16;   // key channels a thread holds of its column
 
 struct ScanArgs {
   const float* qkv;            // [tokens, ld_qkv]: queries, keys (kv head major, D each) and values (head major, V each)
@@ -35,6 +37,8 @@ struct ScanArgs {
   const void* p1;              // matrix memory: bias of zf [H]; delta: A [H]
   int p_dtype;
   float cap, q_scale;
+  float* prep;                 // [tokens, H, rec]: what the scan reads per row and head (see recurrent_prepare_kernel)
+  int rec;
   float* state;
   long long state_stride;      // floats between slots (two copies inside)
   const int* cu_seqlens;
@@ -43,133 +47,183 @@ struct ScanArgs {
   const int* state_phase;
   float* out;                  // [tokens, ld_out], head major, V each
   long long ld_out;
-  int H, G, D, V;
+  int tokens, H, G, D, V;
 };
 
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+// Everything of a row that does not depend on the rows before it, one warp per (row, head), so that the scan's loop is
+// the recurrence alone. Record of rec >= 3 D + 2 floats: keys [D], queries [D], decays [D], two scalars, padding.
+//   matrix memory: keys as they are, queries times q_scale, (no decays), the log gates i and f
+//   delta rule:    unit keys, unit queries times q_scale, g = exp(-exp(A) softplus(a + dt)), beta
+template <int kMode>
+__global__ void recurrent_prepare_kernel(ScanArgs a) {
+  pdl_start();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= a.tokens * a.H) return;
+  const int t = warp / a.H, h = warp - t * a.H, D = a.D;
+  const int g = h / (a.H / a.G);
+  const float* r = a.qkv + (size_t)t * a.ld_qkv;
+  float* rec = a.prep + ((size_t)t * a.H + h) * a.rec;
+  const float* gr = a.gates + (size_t)t * a.ld_gates;
+  if (kMode == kMatrixMemory) {
+    for (int d = lane; d < D; d += 32) {
+      rec[d] = r[a.k_off + g * D + d];
+      rec[D + d] = r[a.q_off + g * D + d] * a.q_scale;
+    }
+    if (lane == 0) {
+      const float zi = gr[a.i_off + h] + load_as_f32(a.p0, a.p_dtype, h), zf = gr[a.f_off + h] + load_as_f32(a.p1, a.p_dtype, h);
+      const float fx = a.cap * tanhf(zf / a.cap);
+      rec[3 * D] = a.cap * tanhf(zi / a.cap);
+      rec[3 * D + 1] = fminf(fx, 0.f) - log1pf(expf(-fabsf(fx)));     // logsigmoid
+    }
+  } else {
+    float k2 = 0.f, q2 = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      const float k = r[a.k_off + g * D + d], q = r[a.q_off + g * D + d];
+      k2 += k * k;
+      q2 += q * q;
+    }
+    k2 = warp_sum(k2);
+    q2 = warp_sum(q2);
+    const float kn = 1.f / sqrtf(k2 + 1e-6f), qn = a.q_scale / sqrtf(q2 + 1e-6f);
+    const float rate = expf(load_as_f32(a.p1, a.p_dtype, h));
+    for (int d = lane; d < D; d += 32) {
+      rec[d] = r[a.k_off + g * D + d] * kn;
+      rec[D + d] = r[a.q_off + g * D + d] * qn;
+      const float x = a.decay[(size_t)t * a.ld_decay + (size_t)h * D + d] + load_as_f32(a.p0, a.p_dtype, (size_t)h * D + d);
+      rec[2 * D + d] = expf(-rate * softplus_f(x));
+    }
+    if (lane == 0) rec[3 * D] = 1.f / (1.f + expf(-gr[a.i_off + h]));
+  }
+}
+
+template <int kBytes>
+__device__ __forceinline__ void cp_async(float* smem, const float* global) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  if (kBytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(global) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(global) : "memory");
+}
+
+template <int kLanes>
 __device__ __forceinline__ float lanes_sum(float v) {
 #pragma unroll
   for (int o = kLanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-template <int kMode, int R>
-__global__ void __launch_bounds__(kLanes* kCols) recurrent_scan_kernel(ScanArgs a) {
+// Block (request, head, slice of kThreads / kLanes value columns): the request's rows of the step in order, the slice of
+// C in registers (a column's D numbers spread over kLanes lanes, R each), the rows' records staged in shared memory a
+// chunk at a time.
+template <int kMode, int kLanes, int R>
+__global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, int chunk) {
   pdl_start();
+  extern __shared__ __align__(16) float stage[];   // two buffers of [chunk][rec] records, then [chunk][cols] values
+  constexpr int kCols = kThreads / kLanes;
   const int b = blockIdx.x, h = blockIdx.y;
   const int start = a.cu_seqlens[b], n_rows = a.cu_seqlens[b + 1] - start;
   if (n_rows <= 0 || a.token_req[start] < 0) return;    // a padding request of a recorded step owns no state
-  const int j = threadIdx.x % kLanes;
-  const int c = blockIdx.z * kCols + threadIdx.x / kLanes;
+  const int j = threadIdx.x % kLanes, cl = threadIdx.x / kLanes;
+  const int c = blockIdx.z * kCols + cl;
   const bool col = c < a.V;
-  const int D = a.D, V = a.V;
-  const int g = h / (a.H / a.G);
+  const int D = a.D, V = a.V, rec = a.rec;
   const int elems = D * V + (kMode == kMatrixMemory ? D + 1 : 0);
   const int phase = a.state_phase[b];
   const float* old = a.state + (size_t)a.state_slots[b] * a.state_stride + ((size_t)phase * a.H + h) * elems;
   float* fresh = a.state + (size_t)a.state_slots[b] * a.state_stride + ((size_t)(1 - phase) * a.H + h) * elems;
-
-  float C[R], nn[R], par[R];   // par: delta: dt of the thread's channels
-  float m = 0.f, p1 = 0.f, p0 = 0.f;
+  float C[R], nn[R];
+  float m = 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int d = j + i * kLanes;
     C[i] = (col && d < D) ? old[(size_t)c * D + d] : 0.f;
-    nn[i] = 0.f;
-    par[i] = 0.f;
-    if (kMode == kMatrixMemory && d < D) nn[i] = old[(size_t)D * V + d];
-    if (kMode == kGatedDelta && d < D) par[i] = load_as_f32(a.p0, a.p_dtype, (size_t)h * D + d);
+    nn[i] = (kMode == kMatrixMemory && d < D) ? old[(size_t)D * V + d] : 0.f;
   }
-  if (kMode == kMatrixMemory) {
-    m = old[(size_t)D * V + D];
-    p0 = load_as_f32(a.p0, a.p_dtype, h);
-    p1 = load_as_f32(a.p1, a.p_dtype, h);
-  } else {
-    p1 = expf(load_as_f32(a.p1, a.p_dtype, h));
-  }
+  if (kMode == kMatrixMemory) m = old[(size_t)D * V + D];
 
-  // the next row's inputs, requested one row ahead
-  float kq[R], qq[R], aa[R], vv = 0.f, z0 = 0.f, z1 = 0.f;
-  auto fetch = [&](int row) {
-    const float* r = a.qkv + (size_t)row * a.ld_qkv;
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int d = j + i * kLanes;
-      kq[i] = d < D ? r[a.k_off + g * D + d] : 0.f;
-      qq[i] = d < D ? r[a.q_off + g * D + d] : 0.f;
-      if (kMode == kGatedDelta) aa[i] = d < D ? a.decay[(size_t)row * a.ld_decay + (size_t)h * D + d] : 0.f;
+  // two buffers: the next chunk's records are on their way (cp.async) while this one is worked on
+  const int buf_floats = chunk * (rec + kCols);
+  auto request = [&](int t0, int buf) {
+    const int n = min(chunk, n_rows - t0), rec4 = rec / 4;
+    float* st = stage + (size_t)buf * buf_floats;
+    float* vl = st + (size_t)chunk * rec;
+    for (int i = threadIdx.x; i < n * rec4; i += kThreads) {
+      const int tt = i / rec4, e = (i - tt * rec4) * 4;
+      cp_async<16>(st + (size_t)tt * rec + e, a.prep + ((size_t)(start + t0 + tt) * a.H + h) * rec + e);
     }
-    vv = col ? r[a.v_off + h * V + c] : 0.f;
-    const float* gr = a.gates + (size_t)row * a.ld_gates;
-    z0 = gr[a.i_off + h];
-    if (kMode == kMatrixMemory) z1 = gr[a.f_off + h];
+    for (int i = threadIdx.x; i < n * kCols; i += kThreads) {
+      const int tt = i / kCols, cc = blockIdx.z * kCols + (i - tt * kCols);
+      if (cc < V) cp_async<4>(vl + i, a.qkv + (size_t)(start + t0 + tt) * a.ld_qkv + a.v_off + h * V + cc);
+      else vl[i] = 0.f;
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  fetch(start);
-  for (int t = 0; t < n_rows; ++t) {
-    float k[R], q[R], dec[R];
-    const float v = vv, zi = z0, zf = z1;
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-      k[i] = kq[i];
-      q[i] = qq[i];
-      if (kMode == kGatedDelta) dec[i] = aa[i];
-    }
-    if (t + 1 < n_rows) fetch(start + t + 1);
-    float o;
-    if (kMode == kMatrixMemory) {
-      const float gi = a.cap * tanhf((zi + p0) / a.cap);
-      const float fx = a.cap * tanhf((zf + p1) / a.cap);
-      const float gf = fminf(fx, 0.f) - log1pf(expf(-fabsf(fx)));     // logsigmoid
-      const float m_new = fmaxf(gf + m, gi);
-      const float keep = expf(gf + m - m_new), put = expf(gi - m_new);
-      m = m_new;
-      float num = 0.f, nq = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const float qs = q[i] * a.q_scale;
-        C[i] = keep * C[i] + put * k[i] * v;
-        nn[i] = keep * nn[i] + put * k[i];
-        num += C[i] * qs;
-        nq += nn[i] * qs;
-      }
-      num = lanes_sum(num);
-      nq = lanes_sum(nq);
-      o = num / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+  request(0, 0);
+  int turn = 0;
+  for (int t0 = 0; t0 < n_rows; t0 += chunk, turn ^= 1) {
+    const int n = min(chunk, n_rows - t0);
+    if (t0 + chunk < n_rows) {
+      request(t0 + chunk, turn ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
     } else {
-      float k2 = 0.f, q2 = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        k2 += k[i] * k[i];
-        q2 += q[i] * q[i];
-      }
-      k2 = lanes_sum(k2);
-      q2 = lanes_sum(q2);
-      const float kn = 1.f / sqrtf(k2 + 1e-6f), qn = a.q_scale / sqrtf(q2 + 1e-6f);
-      const float beta = 1.f / (1.f + expf(-zi));
-      float kv = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        k[i] *= kn;
-        C[i] *= expf(-p1 * softplus_f(dec[i] + par[i]));
-        kv += C[i] * k[i];
-      }
-      kv = lanes_sum(kv);
-      const float d = beta * (v - kv);
-      float num = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        C[i] += k[i] * d;
-        num += C[i] * (q[i] * qn);
-      }
-      o = lanes_sum(num);
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
-    if (j == 0 && col) a.out[(size_t)(start + t) * a.ld_out + (size_t)h * V + c] = o;
+    __syncthreads();
+    const float* stage_now = stage + (size_t)turn * buf_floats;
+    const float* vals = stage_now + (size_t)chunk * rec;
+    for (int tt = 0; tt < n; ++tt) {
+      const float* r = stage_now + (size_t)tt * rec;
+      const float v = vals[tt * kCols + cl];
+      float o;
+      if (kMode == kMatrixMemory) {
+        const float gi = r[3 * D], gf = r[3 * D + 1];
+        const float m_new = fmaxf(gf + m, gi);
+        const float keep = expf(gf + m - m_new), put = expf(gi - m_new);
+        m = m_new;
+        float num = 0.f, nq = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int d = j + i * kLanes;
+          const float k = d < D ? r[d] : 0.f, q = d < D ? r[D + d] : 0.f;
+          C[i] = keep * C[i] + put * k * v;
+          nn[i] = keep * nn[i] + put * k;
+          num += C[i] * q;
+          nq += nn[i] * q;
+        }
+        num = lanes_sum<kLanes>(num);
+        nq = lanes_sum<kLanes>(nq);
+        o = num / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+      } else {
+        const float beta = r[3 * D];
+        float k[R];
+        float kv = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int d = j + i * kLanes;
+          k[i] = d < D ? r[d] : 0.f;
+          C[i] *= d < D ? r[2 * D + d] : 0.f;
+          kv += C[i] * k[i];
+        }
+        kv = lanes_sum<kLanes>(kv);
+        const float dlt = beta * (v - kv);
+        float num = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int d = j + i * kLanes;
+          C[i] += k[i] * dlt;
+          num += C[i] * (d < D ? r[D + d] : 0.f);
+        }
+        o = lanes_sum<kLanes>(num);
+      }
+      if (j == 0 && col) a.out[(size_t)(start + t0 + tt) * a.ld_out + (size_t)h * V + c] = o;
+    }
+    __syncthreads();                           // everyone has read this buffer before the chunk after next is requested into it
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int d = j + i * kLanes;
     if (col && d < D) fresh[(size_t)c * D + d] = C[i];
-    if (kMode == kMatrixMemory && blockIdx.z == 0 && threadIdx.x < kLanes && d < D) fresh[(size_t)D * V + d] = nn[i];
+    if (kMode == kMatrixMemory && blockIdx.z == 0 && cl == 0 && d < D) fresh[(size_t)D * V + d] = nn[i];
   }
   if (kMode == kMatrixMemory && blockIdx.z == 0 && threadIdx.x == 0) fresh[(size_t)D * V + D] = m;
 }
@@ -198,39 +252,58 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, long long ld_out, co
 
 }  // namespace
 
+// floats of scratch the scan wants per row: oi_recurrent_scan's `prep` is [tokens, H, that]
+OI_API int oi_recurrent_record(int D) { return (3 * D + 2 + 3) & ~3; }   // a multiple of four floats: 16-byte copies
+
 // mode 0: matrix memory (p0, p1: the two gate biases [H]); mode 1: gated delta rule (p0: dt [H * D], p1: A [H];
-// decay: a [tokens, ld_decay]). State: [slots][2][H][D * V (+ D + 1 in mode 0)] floats.
+// decay: a [tokens, ld_decay]). State: [slots][2][H][D * V (+ D + 1 in mode 0)] floats. prep: scratch, see above.
 OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q_off, int k_off, int v_off, const float* gates,
                              long long ld_gates, int i_off, int f_off, const float* decay, long long ld_decay, const void* p0,
-                             const void* p1, int p_dtype, float cap, float q_scale, float* state, long long state_stride,
-                             const int* cu_seqlens, const int* token_req, const int* state_slots, const int* state_phase,
-                             float* out, long long ld_out, int requests, int H, int G, int D, int V, void* stream) {
+                             const void* p1, int p_dtype, float cap, float q_scale, float* prep, float* state,
+                             long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots,
+                             const int* state_phase, float* out, long long ld_out, int tokens, int requests, int H, int G, int D,
+                             int V, void* stream) {
   OI_REQUIRE(mode == kMatrixMemory || mode == kGatedDelta, "recurrent_scan: unknown mode %d", mode);
-  OI_REQUIRE(requests >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0, "recurrent_scan: bad sizes H=%d G=%d D=%d V=%d", H, G, D, V);
-  OI_REQUIRE(D <= 16 * kLanes, "recurrent_scan: %d key channels per head, at most %d", D, 16 * kLanes);
+  OI_REQUIRE(requests >= 0 && tokens >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0,
+             "recurrent_scan: bad sizes H=%d G=%d D=%d V=%d", H, G, D, V);
+  OI_REQUIRE(D <= 16 * kMaxRegs, "recurrent_scan: %d key channels per head, at most %d", D, 16 * kMaxRegs);
   OI_REQUIRE(mode != kGatedDelta || decay != nullptr, "recurrent_scan: the delta rule needs its decays");
+  OI_REQUIRE(prep != nullptr, "recurrent_scan: the scratch for the rows' records is missing");
   const long long elems = (long long)D * V + (mode == kMatrixMemory ? D + 1 : 0);
   OI_REQUIRE(state != nullptr && state_stride >= 2 * H * elems, "recurrent_scan: the state needs two copies of %lld floats per head", elems);
-  if (requests == 0) return OI_OK;
+  if (requests == 0 || tokens == 0) return OI_OK;
   ScanArgs a;
   a.qkv = qkv, a.ld_qkv = ld_qkv, a.q_off = q_off, a.k_off = k_off, a.v_off = v_off;
   a.gates = gates, a.ld_gates = ld_gates, a.i_off = i_off, a.f_off = f_off;
   a.decay = decay, a.ld_decay = ld_decay, a.p0 = p0, a.p1 = p1, a.p_dtype = p_dtype, a.cap = cap, a.q_scale = q_scale;
+  a.prep = prep, a.rec = oi_recurrent_record(D);
   a.state = state, a.state_stride = state_stride, a.cu_seqlens = cu_seqlens, a.token_req = token_req;
   a.state_slots = state_slots, a.state_phase = state_phase, a.out = out, a.ld_out = ld_out;
-  a.H = H, a.G = G, a.D = D, a.V = V;
-  const dim3 grid(requests, H, (V + kCols - 1) / kCols);
+  a.tokens = tokens, a.H = H, a.G = G, a.D = D, a.V = V;
   cudaStream_t s = (cudaStream_t)stream;
-  const int r = (D + kLanes - 1) / kLanes;
-#define OI_SCAN(MODE)                                                                                         \
-  do {                                                                                                        \
-    if (r <= 4) oi_launch(recurrent_scan_kernel<MODE, 4>, grid, kLanes * kCols, 0, s, a);                     \
-    else if (r <= 8) oi_launch(recurrent_scan_kernel<MODE, 8>, grid, kLanes * kCols, 0, s, a);                \
-    else oi_launch(recurrent_scan_kernel<MODE, 16>, grid, kLanes * kCols, 0, s, a);                           \
+  const int warps = tokens * H;
+  if (mode == kMatrixMemory) oi_launch(recurrent_prepare_kernel<kMatrixMemory>, (warps + 3) / 4, 128, 0, s, a);
+  else oi_launch(recurrent_prepare_kernel<kGatedDelta>, (warps + 3) / 4, 128, 0, s, a);
+  OI_CHECK_LAUNCH();
+  const int chunk = D <= 64 ? 16 : (D <= 128 ? 8 : 4);   // rows per buffer: two buffers of at most 13 KB
+#define OI_SCAN_AS(MODE, LANES, REGS)                                                                                   \
+  do {                                                                                                                  \
+    constexpr int cols = kThreads / LANES;                                                                              \
+    const dim3 grid(requests, H, (V + cols - 1) / cols);                                                                \
+    const size_t smem = 2 * (size_t)chunk * (a.rec + cols) * sizeof(float);                                                 \
+    oi_launch(recurrent_scan_kernel<MODE, LANES, REGS>, grid, kThreads, smem, s, a, chunk);                             \
+  } while (0)
+#define OI_SCAN(MODE)                                 \
+  do {                                                \
+    if (D <= 16) OI_SCAN_AS(MODE, 4, 4);              \
+    else if (D <= 64) OI_SCAN_AS(MODE, 4, 16);        \
+    else if (D <= 128) OI_SCAN_AS(MODE, 8, 16);       \
+    else OI_SCAN_AS(MODE, 16, 16);                    \
   } while (0)
   if (mode == kMatrixMemory) OI_SCAN(kMatrixMemory);
   else OI_SCAN(kGatedDelta);
 #undef OI_SCAN
+#undef OI_SCAN_AS
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

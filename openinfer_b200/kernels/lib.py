@@ -60,7 +60,8 @@ _SIGNATURES = {
     "oi_xielu": [P, P, I, P, I, L, P],
     "oi_short_conv_strided": [P, I, L, P, I, L, P, I, P, L, P, P, P, P, I, I, I, I, I, I, I, P],
     "oi_glu_act": [P, P, I, I, I, I, I, F, P],
-    "oi_recurrent_scan": [I, P, L, I, I, I, P, L, I, I, P, L, P, P, I, F, F, P, L, P, P, P, P, P, L, I, I, I, I, I, P],
+    "oi_recurrent_scan": [I, P, L, I, I, I, P, L, I, I, P, L, P, P, I, F, F, P, P, L, P, P, P, P, P, L, I, I, I, I, I, I, P],
+    "oi_recurrent_record": [I],
     "oi_head_norm_gate": [P, I, L, P, L, P, L, P, I, I, I, I, I, F, F, P],
     "oi_hyper_step": [P, I, I, I, P, P, F, F, P, P, P, I, P, I, F, F, P, I, P, P],
     "oi_hyper_fanout": [P, P, I, I, I, I, P],

@@ -537,12 +537,15 @@ def recurrent_scan(mode: int, out: torch.Tensor, qkv: torch.Tensor, offsets, gat
     elems = dim * vdim + (dim + 1 if mode == SCAN_MATRIX_MEMORY else 0)
     if state.shape[1:] != (2, heads, elems) or not state.is_contiguous() or p0.dtype != p1.dtype:
         raise KernelError(f"recurrent_scan: state {tuple(state.shape)} is not [slots, 2, {heads}, {elems}]")
-    _lib.check(_lib.load().oi_recurrent_scan(
+    L = _lib.load()
+    tokens = out.shape[0]
+    prep = torch.empty((tokens, heads, L.oi_recurrent_record(dim)), dtype=torch.float32, device=out.device)
+    _lib.check(L.oi_recurrent_scan(
         mode, qkv.data_ptr(), qkv.stride(0), int(offsets[0]), int(offsets[1]), int(offsets[2]), gates.data_ptr(), gates.stride(0),
         int(gate_offsets[0]), int(gate_offsets[1]), _ptr(decay), 0 if decay is None else decay.stride(0), p0.data_ptr(), p1.data_ptr(),
-        _code(p0, "recurrent_scan"), float(cap), float(q_scale), state.data_ptr(), state.stride(0), ctx.cu_seqlens.data_ptr(),
-        ctx.token_req.data_ptr(), ctx.state_slots.data_ptr(), ctx.state_phase.data_ptr(), out.data_ptr(), out.stride(0),
-        ctx.num_requests, heads, kv_heads, dim, vdim, _stream()), "recurrent_scan")
+        _code(p0, "recurrent_scan"), float(cap), float(q_scale), prep.data_ptr(), state.data_ptr(), state.stride(0),
+        ctx.cu_seqlens.data_ptr(), ctx.token_req.data_ptr(), ctx.state_slots.data_ptr(), ctx.state_phase.data_ptr(), out.data_ptr(),
+        out.stride(0), tokens, ctx.num_requests, heads, kv_heads, dim, vdim, _stream()), "recurrent_scan")
     return out
 
 
