@@ -334,7 +334,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           sum *= rstd_s[m];
           up *= rstd_s[m];
         }
-        if (kSiluMul) sum = gate_act<true>(sum, act) * up;
+        if (kSiluMul) sum = glu_act<true>(sum, up, act, unary_p0);   // (the limit of a clamping activation rides in p0)
       }
       float sq = 0.f;
       if constexpr (kEndsBranch) {
@@ -448,7 +448,8 @@ OI_API int oi_gemm_stream_fused(void* out, int out_dtype, long long ldc, const v
   OiStreamEpilogue ep;
   memset(&ep, 0, sizeof(ep));
   if (epilogue) ep = *epilogue;
-  OI_REQUIRE(act >= OI_ACT_NONE && act <= OI_ACT_GELU_TANH, "gemm_stream: unknown activation code %d", act);
+  OI_REQUIRE((act >= OI_ACT_NONE && act <= OI_ACT_GELU_TANH) || (act == OI_ACT_SWIGLU_CLAMP && !epilogue),
+             "gemm_stream: unknown activation code %d", act);
   OI_REQUIRE(M >= 1 && M <= 128, "gemm_stream: M=%d outside 1..128", M);
   OI_REQUIRE(N >= 1 && K >= 8, "gemm_stream: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_stream: K and row strides must be multiples of 8");
@@ -496,6 +497,17 @@ OI_API int oi_gemm_stream_unary(void* out, int out_dtype, long long ldc, const v
   g_unary_act = act, g_unary_p0 = p0, g_unary_p1 = p1;
   const int rc = oi_gemm_stream_fused(out, out_dtype, ldc, x, ldx, W, ldw, M, N, K, cluster_size, OI_ACT_NONE, nullptr, stream);
   g_unary_act = 0;
+  return rc;
+}
+
+// The gate/up product with a gated activation that takes a limit (OI_ACT_SWIGLU_CLAMP), formed where the K slices are
+// added up, as the other gated activations are: out [M, N / 2].
+OI_API int oi_gemm_stream_glu(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W, long long ldw,
+                              int M, int N, int K, int cluster_size, int act, float limit, void* stream) {
+  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH || act == OI_ACT_SWIGLU_CLAMP, "gemm_stream_glu: unknown activation code %d", act);
+  g_unary_p0 = limit;
+  const int rc = oi_gemm_stream_fused(out, out_dtype, ldc, x, ldx, W, ldw, M, N, K, cluster_size, act, nullptr, stream);
+  g_unary_p0 = 0.f;
   return rc;
 }
 

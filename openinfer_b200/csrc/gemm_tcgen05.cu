@@ -102,7 +102,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
       load(half * 128 + 64 + c, u);
       if (row < M) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) g[e] = gate_act<true>(g[e], act) * u[e];
+        for (int e = 0; e < 32; ++e) g[e] = glu_act<true>(g[e], u[e], act, p0);   // (p0: the limit of a clamping activation)
         store_32(C + (size_t)row * ldc + o0 + cc, g, n_out - (o0 + cc));
       }
     }
@@ -504,6 +504,19 @@ OI_API int oi_gemm_tcgen05_pair(void* C, int c_dtype, long long ldc, const void*
   if (c_dtype == OI_BF16) return launch_pair<kPairStages, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
   if (c_dtype == OI_F32) return launch_pair<kPairStages, float>(C, ldc, A, lda, W, ldw, M, N, K, s);
   OI_REQUIRE(false, "gemm_tcgen05_pair: unknown output dtype code %d", c_dtype);
+}
+
+// The gate/up product with any gated activation, the ones that take a limit included (OI_ACT_SWIGLU_CLAMP), in the
+// epilogue: C [M, N / 2]. pair: 256 x 256 tiles by pairs of CTAs, else 128 x 256 by single CTAs. bfloat16, N % 256 == 0.
+OI_API int oi_gemm_tcgen05_glu(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N,
+                               int K, int pair, int act, float limit, void* stream) {
+  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH || act == OI_ACT_SWIGLU_CLAMP, "gemm_tcgen05_glu: unknown activation code %d", act);
+  OI_REQUIRE(M >= 1 && N >= 1 && K >= 8 && N % 256 == 0, "gemm_tcgen05_glu: bad sizes M=%d N=%d K=%d (N %% 256 == 0)", M, N, K);
+  OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_glu: K and row strides must be multiples of 8");
+  OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05_glu: operands must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  return pair ? launch_pair<kPairStages, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s, act, limit)
+              : launch<256, 4, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s, act, limit);
 }
 
 // The plain product with an activation of one argument (OI_ACT_XIELU with its two numbers) applied to the finished

@@ -8,9 +8,12 @@
 //                          then the down projection, each row written to its pair's place
 //   4. moe_combine_kernel  out[row] = sum_j weight[row, j] * y[row * top + j], j ascending
 //
+// Steps of few rows (at most two pairs an expert on average) skip 2 and run 3 pair by pair (moe_gemv_kernel: a warp per
+// output row, the expert's rows read 16 bytes at a time); larger steps take the tiles.
 // Everything a step needs is found on the device (no sizes travel back to the host), so a step of single tokens can be
-// recorded and replayed. A row's sums are formed in ascending k whatever else shares its tile: the result of a row does
-// not depend on the batch. The products add up in float32 on the ordinary pipes.
+// recorded and replayed. A row's sums are formed in the same order whatever else shares its tile: the result of a row does
+// not depend on the batch. The tiles' products run on the tensor cores for bfloat16 operands (mma.sync, float32
+// accumulation) and on the ordinary pipes for float32 and for rows that cannot be read 16 bytes at a time.
 #include "common.cuh"
 
 namespace {
@@ -29,13 +32,21 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
   const int row = blockIdx.x * warps + wi;
   if (row >= rows) return;
   const T* xr = x + (size_t)row * ldx;
-  for (int e = 0; e < E; ++e) {
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc += load_as_f32(w, w_dtype, (size_t)e * K + k) * to_f32(xr[k]);
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      z[e] = acc;
-      taken[e] = 0;
+  for (int e0 = 0; e0 < E; e0 += 4) {          // four experts at a time: their loads are in flight together
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = lane; k < K; k += 32) {
+      const float xv = to_f32(xr[k]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (e0 + i < E) acc[i] += load_as_f32(w, w_dtype, (size_t)(e0 + i) * K + k) * xv;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float sum = warp_sum(acc[i]);
+      if (lane == 0 && e0 + i < E) {
+        z[e0 + i] = sum;
+        taken[e0 + i] = 0;
+      }
     }
   }
   __syncwarp();
@@ -148,7 +159,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
                                                        long long w_expert_stride, TO* __restrict__ out, long long ld_out, int scatter,
                                                        const int* __restrict__ sorted, const int* __restrict__ tile_info,
                                                        int max_tiles, int N, int K, float limit) {
-  pdl_start();
+  pdl_wait();    // no early trigger: waiting blocks of the next kernel would share the SMs with this product
   const int tile = blockIdx.x;
   if (tile >= tile_info[3 * max_tiles]) return;
   const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = tile_info[3 * tile + 2];
@@ -249,6 +260,146 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
   }
 }
 
+// The tiles' products on the tensor cores for bfloat16 operands that can be read 16 bytes at a time (mma.sync m16n8k16,
+// float32 accumulation): 8 warps, warp w the 16 rows (w & 1) x the 16 columns (w >> 1) of the 32 x 64 tile (and the same
+// columns of the up rows). Operand tiles lie in shared memory as they lie in global memory (rows of 32 k, padded to 40).
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TO, bool kGlu>
+__global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, int a_div, const bf16* __restrict__ Wt,
+                                                           long long w_expert_stride, TO* __restrict__ out, long long ld_out,
+                                                           int scatter, const int* __restrict__ sorted,
+                                                           const int* __restrict__ tile_info, int max_tiles, int N, int K, float limit) {
+  pdl_wait();
+  const int tile = blockIdx.x;
+  if (tile >= tile_info[3 * max_tiles]) return;
+  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = tile_info[3 * tile + 2];
+  const int n0 = blockIdx.y * kTileN;
+  constexpr int kPad = kTileK + 8;
+  __shared__ __align__(16) bf16 As[kTileM][kPad];
+  __shared__ __align__(16) bf16 Bg[kTileN][kPad];
+  __shared__ __align__(16) bf16 Bu[kGlu ? kTileN : 1][kPad];
+  __shared__ int src[kTileM];
+  if (threadIdx.x < kTileM) {
+    int r = -1;
+    if ((int)threadIdx.x < m_rows) {
+      const int place = place0 + threadIdx.x;
+      r = a_div > 0 ? sorted[place] / a_div : place;
+    }
+    src[threadIdx.x] = r;
+  }
+  __syncthreads();
+  const bf16* We = Wt + (size_t)e * w_expert_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const int wm = (warp & 1) * 16, wn = (warp >> 1) * 16;
+  float acc[2][4] = {}, accu[2][4] = {};
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    if (threadIdx.x < kTileM * 4) {
+      const int m = threadIdx.x >> 2, k = (threadIdx.x & 3) * 8;
+      const int r = src[m];
+      *reinterpret_cast<uint4*>(&As[m][k]) = (r >= 0 && k0 + k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)r * lda + k0 + k) : zero;
+    }
+    {
+      const int n = threadIdx.x >> 2, k = (threadIdx.x & 3) * 8;
+      const bool ok = n0 + n < N && k0 + k < K;
+      *reinterpret_cast<uint4*>(&Bg[n][k]) = ok ? *reinterpret_cast<const uint4*>(We + (size_t)(n0 + n) * K + k0 + k) : zero;
+      if (kGlu) *reinterpret_cast<uint4*>(&Bu[n][k]) = ok ? *reinterpret_cast<const uint4*>(We + (size_t)(N + n0 + n) * K + k0 + k) : zero;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; kk += 16) {
+      unsigned a[4];
+      a[0] = *reinterpret_cast<const unsigned*>(&As[wm + g][kk + 2 * tg]);
+      a[1] = *reinterpret_cast<const unsigned*>(&As[wm + g + 8][kk + 2 * tg]);
+      a[2] = *reinterpret_cast<const unsigned*>(&As[wm + g][kk + 2 * tg + 8]);
+      a[3] = *reinterpret_cast<const unsigned*>(&As[wm + g + 8][kk + 2 * tg + 8]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        unsigned b[2];
+        b[0] = *reinterpret_cast<const unsigned*>(&Bg[wn + 8 * j + g][kk + 2 * tg]);
+        b[1] = *reinterpret_cast<const unsigned*>(&Bg[wn + 8 * j + g][kk + 2 * tg + 8]);
+        mma_bf16_16816(acc[j], a, b);
+        if (kGlu) {
+          b[0] = *reinterpret_cast<const unsigned*>(&Bu[wn + 8 * j + g][kk + 2 * tg]);
+          b[1] = *reinterpret_cast<const unsigned*>(&Bu[wn + 8 * j + g][kk + 2 * tg + 8]);
+          mma_bf16_16816(accu[j], a, b);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int m = wm + g + (c >> 1) * 8, n = n0 + wn + 8 * j + 2 * tg + (c & 1);
+      if (m >= m_rows || n >= N) continue;
+      const int place = place0 + m;
+      const size_t row = scatter ? (size_t)sorted[place] : (size_t)place;
+      float v = acc[j][c];
+      if (kGlu) {
+        const float gc = fminf(v, limit), uc = fminf(fmaxf(accu[j][c], -limit), limit);
+        v = gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f);
+      }
+      out[row * ld_out + n] = from_f32<TO>(v);
+    }
+}
+
+// The same two products for steps of few rows (at most two pairs an expert on average): one block per (pair, 16 output
+// rows), a warp per output row at a time, the pair's input row in shared memory as float32, the expert's rows read 16 bytes
+// at a time. No grouping is needed: pair p reads row p / a_div (a_div 0: row p) and writes row p.
+template <typename T, typename TO, bool kGlu>
+__global__ void __launch_bounds__(128) moe_gemv_kernel(const T* __restrict__ A, long long lda, int a_div, const T* __restrict__ Wt,
+                                                       long long w_expert_stride, TO* __restrict__ out, long long ld_out,
+                                                       const int* __restrict__ ids, int N, int K, float limit) {
+  pdl_wait();    // no early trigger: waiting blocks of the next kernel would share the SMs with this product
+  extern __shared__ __align__(16) float xs[];
+  constexpr int kVec = 16 / (int)sizeof(T), kRows = 16;
+  const int p = blockIdx.x, lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+  const T* xr = A + (size_t)(a_div > 0 ? p / a_div : p) * lda;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32(xr[k]);
+  __syncthreads();
+  const T* We = Wt + (size_t)ids[p] * w_expert_stride;
+  const bool vec = K % kVec == 0 && ((uintptr_t)We % 16 == 0);
+  for (int n = blockIdx.y * kRows + wi; n < min(N, (int)(blockIdx.y + 1) * kRows); n += 4) {
+    const T* wg = We + (size_t)n * K;
+    const T* wu = We + (size_t)(N + n) * K;
+    float g = 0.f, u = 0.f;
+    if (vec) {
+      for (int k = lane * kVec; k < K; k += 32 * kVec) {
+        T a[kVec], b[kVec];
+        *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(wg + k);
+        if (kGlu) *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(wu + k);
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          g += to_f32(a[e]) * xs[k + e];
+          if (kGlu) u += to_f32(b[e]) * xs[k + e];
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        g += to_f32(wg[k]) * xs[k];
+        if (kGlu) u += to_f32(wu[k]) * xs[k];
+      }
+    }
+    g = warp_sum(g);
+    if (kGlu) u = warp_sum(u);
+    if (lane == 0) {
+      float v = g;
+      if (kGlu) {
+        const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+        v = gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f);
+      }
+      out[(size_t)p * ld_out + n] = from_f32<TO>(v);
+    }
+  }
+}
+
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts, int top, int W,
                                    size_t n) {
   pdl_start();
@@ -263,6 +414,9 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
 }  // namespace
 
 OI_API int oi_moe_max_tiles(int pairs, int experts) { return pairs / kTileM + experts; }
+
+// Steps of at most this many (row, choice) pairs take the row-by-row products and need no grouping.
+OI_API int oi_moe_small(int pairs, int experts) { return pairs <= 2 * experts && pairs <= 64; }
 
 // x [rows, K] (row stride ldx) in `dtype`; router weights [E, K]; ids, wts [rows, top]; sorted [rows * top];
 // tile_info [3 * max_tiles + 1] with max_tiles = oi_moe_max_tiles(rows * top, E).
@@ -283,6 +437,7 @@ OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_r
     OI_REQUIRE(false, "moe_route: unknown dtype code %d", dtype);
   OI_CHECK_LAUNCH();
   const int pairs = rows * top;
+  if (oi_moe_small(pairs, E)) return OI_OK;      // few rows: the products go pair by pair and need no grouping
   oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E));
   OI_CHECK_LAUNCH();
   return OI_OK;
@@ -291,12 +446,36 @@ OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_r
 // act [rows * top, F] (scratch, `dtype`), y [rows * top, W] float32 (scratch), out [rows, W] float32.
 // w_gate_up [E, 2 F, W] (F gate rows, then F up rows), w_down [E, W, F], both in `dtype`.
 OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows, int W, int F,
-                          int E, int top, float limit, const int* sorted, const int* tile_info, const float* wts, void* act, float* y,
-                          float* out, void* stream) {
+                          int E, int top, float limit, const int* ids, const int* sorted, const int* tile_info, const float* wts,
+                          void* act, float* y, float* out, void* stream) {
   OI_REQUIRE(rows >= 0 && W > 0 && F > 0 && E > 0 && top > 0, "moe_experts: bad sizes");
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int pairs = rows * top, max_tiles = oi_moe_max_tiles(pairs, E);
+  const size_t n_out = (size_t)rows * W;
+  const int cblocks = (int)((n_out + 255) / 256 > 148 * 16 ? 148 * 16 : (n_out + 255) / 256);
+  if (oi_moe_small(pairs, E) && (size_t)(W > F ? W : F) * sizeof(float) <= 48 * 1024) {
+    const dim3 v1(pairs, (F + 15) / 16), v2(pairs, (W + 15) / 16);
+    if (dtype == OI_F32) {
+      oi_launch(moe_gemv_kernel<float, float, true>, v1, 128, (size_t)W * 4, s, (const float*)x, ldx, top, (const float*)w_gate_up,
+                (long long)2 * F * W, (float*)act, (long long)F, ids, F, W, limit);
+      OI_CHECK_LAUNCH();
+      oi_launch(moe_gemv_kernel<float, float, false>, v2, 128, (size_t)F * 4, s, (const float*)act, (long long)F, 0, (const float*)w_down,
+                (long long)W * F, y, (long long)W, ids, W, F, 0.f);
+    } else if (dtype == OI_BF16) {
+      oi_launch(moe_gemv_kernel<bf16, bf16, true>, v1, 128, (size_t)W * 4, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up,
+                (long long)2 * F * W, (bf16*)act, (long long)F, ids, F, W, limit);
+      OI_CHECK_LAUNCH();
+      oi_launch(moe_gemv_kernel<bf16, float, false>, v2, 128, (size_t)F * 4, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down,
+                (long long)W * F, y, (long long)W, ids, W, F, 0.f);
+    } else {
+      OI_REQUIRE(false, "moe_experts: unknown dtype code %d", dtype);
+    }
+    OI_CHECK_LAUNCH();
+    oi_launch(moe_combine_kernel, cblocks, 256, 0, s, out, (const float*)y, wts, top, W, n_out);
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   const dim3 g1(max_tiles, (F + kTileN - 1) / kTileN), g2(max_tiles, (W + kTileN - 1) / kTileN);
   if (dtype == OI_F32) {
     oi_launch(moe_gemm_kernel<float, float, true>, g1, 256, 0, s, (const float*)x, ldx, top, (const float*)w_gate_up, (long long)2 * F * W,
@@ -305,11 +484,22 @@ OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w
     oi_launch(moe_gemm_kernel<float, float, false>, g2, 256, 0, s, (const float*)act, (long long)F, 0, (const float*)w_down, (long long)W * F,
               y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
   } else if (dtype == OI_BF16) {
-    oi_launch(moe_gemm_kernel<bf16, bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
-              (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+    // tensor cores when every row of the operands starts on a 16-byte boundary
+    const bool tc1 = W % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_gate_up % 16 == 0;
+    const bool tc2 = F % 8 == 0 && (uintptr_t)act % 16 == 0 && (uintptr_t)w_down % 16 == 0;
+    if (tc1)
+      oi_launch(moe_gemm_mma_kernel<bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
+                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+    else
+      oi_launch(moe_gemm_kernel<bf16, bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
+                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
     OI_CHECK_LAUNCH();
-    oi_launch(moe_gemm_kernel<bf16, float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
-              y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+    if (tc2)
+      oi_launch(moe_gemm_mma_kernel<float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
+                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+    else
+      oi_launch(moe_gemm_kernel<bf16, float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
+                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
   } else {
     OI_REQUIRE(false, "moe_experts: unknown dtype code %d", dtype);
   }

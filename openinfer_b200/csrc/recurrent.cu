@@ -117,7 +117,7 @@ __device__ __forceinline__ float lanes_sum(float v) {
 // chunk at a time.
 template <int kMode, int kLanes, int R>
 __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, int chunk) {
-  pdl_start();
+  pdl_wait();    // no early trigger: the blocks of the kernel behind this one would wait on the SMs this latency-bound loop needs
   extern __shared__ __align__(16) float stage[];   // two buffers of [chunk][rec] records, then [chunk][cols] values
   constexpr int kCols = kThreads / kLanes;
   const int b = blockIdx.x, h = blockIdx.y;

@@ -68,7 +68,10 @@ _SIGNATURES = {
     "oi_scaled_sum": [P, P, P, F, F, L, P],
     "oi_moe_max_tiles": [I, I],
     "oi_moe_route": [P, I, L, P, I, I, I, I, I, P, P, P, P, P],
-    "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, P, P, P, P, P, P, P],
+    "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P],
+    "oi_moe_small": [I, I],
+    "oi_gemm_stream_glu": [P, I, L, P, L, P, L, I, I, I, I, I, F, P],
+    "oi_gemm_tcgen05_glu": [P, L, P, L, P, L, I, I, I, I, I, F, P],
 }
 
 

@@ -653,6 +653,6 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     y = torch.empty((rows * top, W), dtype=torch.float32, device=x.device)
     out = torch.empty((rows, W), dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().oi_moe_experts(x.data_ptr(), _code(x, "moe_experts"), x.stride(0), w_gate_up.data_ptr(), w_down.data_ptr(), rows,
-                                          W, F2 // 2, E, top, float(limit), order.data_ptr(), tiles.data_ptr(), wts.data_ptr(),
+                                          W, F2 // 2, E, top, float(limit), ids.data_ptr(), order.data_ptr(), tiles.data_ptr(), wts.data_ptr(),
                                           act.data_ptr(), y.data_ptr(), out.data_ptr(), _stream()), "moe_experts")
     return out

@@ -46,12 +46,32 @@ class GatedMlp(FeedForward):
         # Rows of the fused matrix: blocks of `block` gate rows followed by the up rows of the same
         # indices. With block = 64 a 128-row tile of the tensor-core products holds a gate block and
         # its up block side by side, and the activation is formed in those kernels' epilogues.
-        self.block = gemm_tcgen05.ACT_BLOCK if (self.fused and g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
+        self.block = gemm_tcgen05.ACT_BLOCK if (g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
         nb = inter // self.block
         self.w_gate_up = torch.stack([g.view(nb, self.block, -1), u.view(nb, self.block, -1)], dim=1).reshape(2 * inter, -1).contiguous()
         self.w_down = tensors[self.spec.down_name].contiguous()
 
     takes_out_dtype = True
+
+    def _gate_up_with_activation(self, act: torch.Tensor, x: torch.Tensor, L) -> bool:
+        """act = activation(gate, up) by ONE product kernel, when one takes the operands."""
+        from ..kernels import policy
+        s = self.spec
+        M, N, K = x.shape[0], self.w_gate_up.shape[0], x.shape[1]
+        if (x.dtype != torch.bfloat16 or self.w_gate_up.dtype != torch.bfloat16 or self.block != gemm_tcgen05.ACT_BLOCK or K % 8
+                or x.data_ptr() % 16 or policy.batch_invariant()):
+            return False
+        if M <= 32 and N % 128 == 0:
+            _lib.check(L.oi_gemm_stream_glu(act.data_ptr(), 1, act.stride(0), x.data_ptr(), x.stride(0), self.w_gate_up.data_ptr(),
+                                            self.w_gate_up.stride(0), M, N, K, L.oi_stream_slices(N, K), self.act_code, float(s.limit),
+                                            _lib.current_stream()), "gemm_stream_glu")
+            return True
+        if M >= 128 and N % 256 == 0:
+            _lib.check(L.oi_gemm_tcgen05_glu(act.data_ptr(), act.stride(0), x.data_ptr(), x.stride(0), self.w_gate_up.data_ptr(),
+                                             self.w_gate_up.stride(0), M, N, K, 1 if M >= 2048 else 0, self.act_code, float(s.limit),
+                                             _lib.current_stream()), "gemm_tcgen05_glu")
+            return True
+        return False
 
     def forward(self, x: torch.Tensor, ctx, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """One native call (``oi_gated_mlp``): it picks, by the step's rows, the product that forms the activation in
@@ -66,8 +86,13 @@ class GatedMlp(FeedForward):
         if M > 32:
             ensure_library(x.device)
         if not self.fused or out_dtype not in (None, x.dtype):
-            gate_up = linear(x, self.w_gate_up)
-            act = ops.glu_act(torch.empty((M, inter), dtype=x.dtype, device=x.device), gate_up, self.block, s.activation, s.limit)
+            # an activation with a limit, or a float32 result: the gate/up product with the activation in its epilogue where
+            # a hand-written product takes the shape (the weight stream up to 32 rows, tcgen05 tiles from 128), else the
+            # plain product and the activation kernel; then the down projection
+            act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+            if not self._gate_up_with_activation(act, x, L):
+                gate_up = linear(x, self.w_gate_up)
+                ops.glu_act(act, gate_up, self.block, s.activation, s.limit)
             return linear(act, self.w_down, out_dtype=out_dtype)
         out = torch.empty((M, s.hidden_size), dtype=x.dtype, device=x.device)
         act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
