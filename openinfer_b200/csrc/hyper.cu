@@ -13,7 +13,8 @@ constexpr int kMaxStreams = 8;
 // X [rows, S, W]. Part 1 (y != null): the streams of the row are mixed and y is added (y2 != null: y = c1 y + c2 y2).
 // Part 2 (out != null): out[row] = u * rsqrt(mean(u^2) + eps) * (w_offset + w), u = sum_s a[s] x_s (a null: the plain sum).
 // row_idx (part 2 alone): output row r reads the streams of row row_idx[r].
-template <typename TO>
+// kVec: columns a thread handles side by side (4: 16-byte accesses, for widths that are a multiple of four).
+template <typename TO, int kVec>
 __global__ void hyper_step_kernel(float* __restrict__ X, int S, int W, const float* __restrict__ y, const float* __restrict__ y2,
                                   float c1, float c2, const void* __restrict__ mix, const void* __restrict__ b_out,
                                   const void* __restrict__ a_in, int p_dtype, const void* __restrict__ norm_w, int nw_dtype,
@@ -29,47 +30,87 @@ __global__ void hyper_step_kernel(float* __restrict__ X, int S, int W, const flo
   }
   __syncthreads();
   float* xr = X + (size_t)row * S * W;
+  auto load = [&](const float* p, float (&v)[kVec]) {
+    if (kVec == 4) {
+      const float4 t = *reinterpret_cast<const float4*>(p);
+      v[0] = t.x, v[1] = t.y, v[2] = t.z, v[kVec - 1] = t.w;
+    } else {
+      v[0] = *p;
+    }
+  };
+  auto store = [&](float* p, const float (&v)[kVec]) {
+    if (kVec == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[kVec - 1]);
+    else *p = v[0];
+  };
   float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float x[kMaxStreams];
+  for (int c = threadIdx.x * kVec; c < W; c += blockDim.x * kVec) {
+    float x[kMaxStreams][kVec];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? xr[(size_t)s * W + c] : 0.f;
+    for (int s = 0; s < kMaxStreams; ++s) {
+      if (s < S) load(xr + (size_t)s * W + c, x[s]);
+      else
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) x[s][e] = 0.f;
+    }
     if (y) {
-      float yv = y[(size_t)row * W + c];
-      if (y2) yv = c1 * yv + c2 * y2[(size_t)row * W + c];
-      float nx[kMaxStreams];
+      float yv[kVec];
+      load(y + (size_t)row * W + c, yv);
+      if (y2) {
+        float y2v[kVec];
+        load(y2 + (size_t)row * W + c, y2v);
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) yv[e] = c1 * yv[e] + c2 * y2v[e];
+      }
+      float nx[kMaxStreams][kVec];
 #pragma unroll
       for (int r = 0; r < kMaxStreams; ++r) {
-        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) nx[r][e] = 0.f;
         if (r < S) {
 #pragma unroll
           for (int s = 0; s < kMaxStreams; ++s)
-            if (s < S) acc += sM[s * S + r] * x[s];
-          acc += sB[r] * yv;
-          xr[(size_t)r * W + c] = acc;
+            if (s < S)
+#pragma unroll
+              for (int e = 0; e < kVec; ++e) nx[r][e] += sM[s * S + r] * x[s][e];
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) nx[r][e] += sB[r] * yv[e];
+          store(xr + (size_t)r * W + c, nx[r]);
         }
-        nx[r] = acc;
       }
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s) x[s] = nx[s];
+      for (int s = 0; s < kMaxStreams; ++s)
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) x[s][e] = nx[s][e];
     }
     if (out) {
-      float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) u += sA[s] * x[s];
-      ss += u * u;
+      for (int e = 0; e < kVec; ++e) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s)
+          if (s < S) u += sA[s] * x[s][e];
+        ss += u * u;
+      }
     }
   }
   if (!out) return;
   ss = block_sum(ss, red);
   const float r = 1.f / sqrtf(ss / (float)W + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {   // the thread reads back what it wrote itself
-    float u = 0.f;
+  for (int c = threadIdx.x * kVec; c < W; c += blockDim.x * kVec) {   // the thread reads back what it wrote itself
+    float u[kVec];
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) u[e] = 0.f;
 #pragma unroll
     for (int s = 0; s < kMaxStreams; ++s)
-      if (s < S) u += sA[s] * xr[(size_t)s * W + c];
-    out[(size_t)row_out * W + c] = from_f32<TO>(u * r * (w_offset + load_as_f32(norm_w, nw_dtype, c)));
+      if (s < S) {
+        float xv[kVec];
+        load(xr + (size_t)s * W + c, xv);
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) u[e] += sA[s] * xv[e];
+      }
+#pragma unroll
+    for (int e = 0; e < kVec; ++e)
+      out[(size_t)row_out * W + c + e] = from_f32<TO>(u[e] * r * (w_offset + load_as_f32(norm_w, nw_dtype, c + e)));
   }
 }
 
@@ -103,14 +144,21 @@ OI_API int oi_hyper_step(float* X, int rows, int S, int W, const float* y, const
   OI_REQUIRE(row_idx == nullptr || y == nullptr, "hyper_step: rows are gathered for reading only");
   OI_REQUIRE(out == nullptr || norm_w != nullptr, "hyper_step: the norm needs its weight");
   if (rows == 0) return OI_OK;
-  const int threads = W >= 1024 ? 256 : (W >= 256 ? 128 : 64);
+  const bool vec = W % 4 == 0 && (uintptr_t)X % 16 == 0 && (y == nullptr || (uintptr_t)y % 16 == 0) && (y2 == nullptr || (uintptr_t)y2 % 16 == 0);
+  const int cols = vec ? W / 4 : W;
+  const int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
-  if (out_dtype == OI_BF16 && out != nullptr)
-    oi_launch(hyper_step_kernel<bf16>, rows, threads, 0, s, X, S, W, y, y2, c1, c2, mix, b_out, a_in, p_dtype, norm_w, nw_dtype, eps,
-              w_offset, (bf16*)out, row_idx);
-  else
-    oi_launch(hyper_step_kernel<float>, rows, threads, 0, s, X, S, W, y, y2, c1, c2, mix, b_out, a_in, p_dtype, norm_w, nw_dtype, eps,
-              w_offset, (float*)out, row_idx);
+#define OI_HYPER(TO, VEC)                                                                                                  \
+  oi_launch(hyper_step_kernel<TO, VEC>, rows, threads, 0, s, X, S, W, y, y2, c1, c2, mix, b_out, a_in, p_dtype, norm_w, nw_dtype, \
+            eps, w_offset, (TO*)out, row_idx)
+  if (out_dtype == OI_BF16 && out != nullptr) {
+    if (vec) OI_HYPER(bf16, 4);
+    else OI_HYPER(bf16, 1);
+  } else {
+    if (vec) OI_HYPER(float, 4);
+    else OI_HYPER(float, 1);
+  }
+#undef OI_HYPER
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

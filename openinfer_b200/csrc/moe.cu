@@ -1,6 +1,6 @@
 // Routed experts: a feed-forward of `experts` small gated layers of which every row uses `top`.
 //
-//   1. moe_router_kernel   z = W_r x in float32 (one warp a row), the `top` largest logits (ties to the lower index),
+//   1. moe_router_kernel   z = W_r x in float32 (one block a row), the `top` largest logits (ties to the lower index),
 //                          their softmax -> ids [rows, top], weights [rows, top]
 //   2. moe_group_kernel    the (row, choice) pairs sorted by expert (stable, so the order never depends on timing), and
 //                          the list of row tiles (expert, first sorted place, rows) the products run over
@@ -25,15 +25,16 @@ template <typename T>
 __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w, int w_dtype, int rows, int K,
                                   int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
   pdl_start();
-  extern __shared__ float smem[];
+  extern __shared__ float smem[];              // the row's logits [E], then which of them are taken [E bytes]
   const int warps = blockDim.x >> 5, wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* z = smem + (size_t)wi * E;
-  unsigned char* taken = reinterpret_cast<unsigned char*>(smem + (size_t)warps * E) + (size_t)wi * E;
-  const int row = blockIdx.x * warps + wi;
-  if (row >= rows) return;
+  float* z = smem;
+  unsigned char* taken = reinterpret_cast<unsigned char*>(smem + E);
+  const int row = blockIdx.x;
   const T* xr = x + (size_t)row * ldx;
-  for (int e0 = 0; e0 < E; e0 += 4) {          // four experts at a time: their loads are in flight together
+  // one block a row; a warp takes four experts at a time, so that their loads are in flight together
+  for (int e0 = wi * 4; e0 < E; e0 += warps * 4) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (int k = lane; k < K; k += 32) {
       const float xv = to_f32(xr[k]);
 #pragma unroll
@@ -49,7 +50,8 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
       }
     }
   }
-  __syncwarp();
+  __syncthreads();
+  if (wi != 0) return;
   float chosen_z[kMaxTop];
   int chosen_e[kMaxTop];
   for (int j = 0; j < top; ++j) {
@@ -427,12 +429,11 @@ OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_r
   OI_REQUIRE(E <= 4096, "moe_route: %d experts, at most 4096", E);
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float) + (size_t)warps * E + 16;
+  const size_t smem = (size_t)E * sizeof(float) + (size_t)E + 16;
   if (dtype == OI_F32)
-    oi_launch(moe_router_kernel<float>, (rows + warps - 1) / warps, warps * 32, smem, s, (const float*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+    oi_launch(moe_router_kernel<float>, rows, 128, smem, s, (const float*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
   else if (dtype == OI_BF16)
-    oi_launch(moe_router_kernel<bf16>, (rows + warps - 1) / warps, warps * 32, smem, s, (const bf16*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+    oi_launch(moe_router_kernel<bf16>, rows, 128, smem, s, (const bf16*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
   else
     OI_REQUIRE(false, "moe_route: unknown dtype code %d", dtype);
   OI_CHECK_LAUNCH();

@@ -115,7 +115,32 @@ __device__ __forceinline__ float lanes_sum(float v) {
 // Block (request, head, slice of kThreads / kLanes value columns): the request's rows of the step in order, the slice of
 // C in registers (a column's D numbers spread over kLanes lanes, R each), the rows' records staged in shared memory a
 // chunk at a time.
-template <int kMode, int kLanes, int R>
+// Which key channel register i of lane j holds, and a row's D numbers into a thread's R registers. kVec4 (D a multiple of
+// four): a lane holds runs of four neighbours, d = 4 (j + (i / 4) kLanes) + i % 4, and reads them 16 bytes at a time;
+// otherwise d = j + i kLanes.
+template <int kLanes, bool kVec4>
+__device__ __forceinline__ int channel_of(int i, int j) {
+  return kVec4 ? 4 * (j + (i >> 2) * kLanes) + (i & 3) : j + i * kLanes;
+}
+template <int kLanes, int R, bool kVec4>
+__device__ __forceinline__ void load_channels(float (&dst)[R], const float* __restrict__ row, int D, int j) {
+  if (kVec4) {
+#pragma unroll
+    for (int q = 0; q < R / 4; ++q) {
+      const int d = 4 * (j + q * kLanes);
+      const float4 v = d < D ? *reinterpret_cast<const float4*>(row + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+      dst[4 * q] = v.x, dst[4 * q + 1] = v.y, dst[4 * q + 2] = v.z, dst[4 * q + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int d = j + i * kLanes;
+      dst[i] = d < D ? row[d] : 0.f;
+    }
+  }
+}
+
+template <int kMode, int kLanes, int R, bool kVec4>
 __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, int chunk) {
   pdl_wait();    // no early trigger: the blocks of the kernel behind this one would wait on the SMs this latency-bound loop needs
   extern __shared__ __align__(16) float stage[];   // two buffers of [chunk][rec] records, then [chunk][cols] values
@@ -135,7 +160,7 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
   float m = 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int d = j + i * kLanes;
+    const int d = channel_of<kLanes, kVec4>(i, j);
     C[i] = (col && d < D) ? old[(size_t)c * D + d] : 0.f;
     nn[i] = (kMode == kMatrixMemory && d < D) ? old[(size_t)D * V + d] : 0.f;
   }
@@ -171,6 +196,7 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
     __syncthreads();
     const float* stage_now = stage + (size_t)turn * buf_floats;
     const float* vals = stage_now + (size_t)chunk * rec;
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       const float* r = stage_now + (size_t)tt * rec;
       const float v = vals[tt * kCols + cl];
@@ -180,40 +206,41 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
         const float m_new = fmaxf(gf + m, gi);
         const float keep = expf(gf + m - m_new), put = expf(gi - m_new);
         m = m_new;
-        float num = 0.f, nq = 0.f;
+        float k[R], q[R];
+        load_channels<kLanes, R, kVec4>(k, r, D, j);
+        load_channels<kLanes, R, kVec4>(q, r + D, D, j);
+        float num[4] = {0.f, 0.f, 0.f, 0.f}, nq[4] = {0.f, 0.f, 0.f, 0.f};     // four partial sums: short dependent chains
+        const float pv = put * v;
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-          const int d = j + i * kLanes;
-          const float k = d < D ? r[d] : 0.f, q = d < D ? r[D + d] : 0.f;
-          C[i] = keep * C[i] + put * k * v;
-          nn[i] = keep * nn[i] + put * k;
-          num += C[i] * q;
-          nq += nn[i] * q;
+          C[i] = keep * C[i] + pv * k[i];
+          nn[i] = keep * nn[i] + put * k[i];
+          num[i & 3] += C[i] * q[i];
+          nq[i & 3] += nn[i] * q[i];
         }
-        num = lanes_sum<kLanes>(num);
-        nq = lanes_sum<kLanes>(nq);
-        o = num / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+        const float ns = lanes_sum<kLanes>((num[0] + num[1]) + (num[2] + num[3]));
+        const float qs = lanes_sum<kLanes>((nq[0] + nq[1]) + (nq[2] + nq[3]));
+        o = ns / (fmaxf(fabsf(qs), expf(-m)) + 1e-6f);
       } else {
         const float beta = r[3 * D];
-        float k[R];
-        float kv = 0.f;
+        float k[R], g[R], q[R];
+        load_channels<kLanes, R, kVec4>(k, r, D, j);
+        load_channels<kLanes, R, kVec4>(g, r + 2 * D, D, j);
+        float kv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-          const int d = j + i * kLanes;
-          k[i] = d < D ? r[d] : 0.f;
-          C[i] *= d < D ? r[2 * D + d] : 0.f;
-          kv += C[i] * k[i];
+          C[i] *= g[i];
+          kv[i & 3] += C[i] * k[i];
         }
-        kv = lanes_sum<kLanes>(kv);
-        const float dlt = beta * (v - kv);
-        float num = 0.f;
+        load_channels<kLanes, R, kVec4>(q, r + D, D, j);
+        const float dlt = beta * (v - lanes_sum<kLanes>((kv[0] + kv[1]) + (kv[2] + kv[3])));
+        float num[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-          const int d = j + i * kLanes;
           C[i] += k[i] * dlt;
-          num += C[i] * (d < D ? r[D + d] : 0.f);
+          num[i & 3] += C[i] * q[i];
         }
-        o = lanes_sum<kLanes>(num);
+        o = lanes_sum<kLanes>((num[0] + num[1]) + (num[2] + num[3]));
       }
       if (j == 0 && col) a.out[(size_t)(start + t0 + tt) * a.ld_out + (size_t)h * V + c] = o;
     }
@@ -221,7 +248,7 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int d = j + i * kLanes;
+    const int d = channel_of<kLanes, kVec4>(i, j);
     if (col && d < D) fresh[(size_t)c * D + d] = C[i];
     if (kMode == kMatrixMemory && blockIdx.z == 0 && cl == 0 && d < D) fresh[(size_t)D * V + d] = nn[i];
   }
@@ -291,7 +318,11 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
     constexpr int cols = kThreads / LANES;                                                                              \
     const dim3 grid(requests, H, (V + cols - 1) / cols);                                                                \
     const size_t smem = 2 * (size_t)chunk * (a.rec + cols) * sizeof(float);                                                 \
-    oi_launch(recurrent_scan_kernel<MODE, LANES, REGS>, grid, kThreads, smem, s, a, chunk);                             \
+    /* plain stream order: launched early, the few long-lived blocks would be packed onto the SMs that the kernel */     \
+    /* before frees first and share their issue slots (measured 2.1 against 0.9 ms for 2,048 rows) */                   \
+    oi_fence_next_launch();                                                                                              \
+    if (D % 4 == 0) oi_launch(recurrent_scan_kernel<MODE, LANES, REGS, true>, grid, kThreads, smem, s, a, chunk);        \
+    else oi_launch(recurrent_scan_kernel<MODE, LANES, REGS, false>, grid, kThreads, smem, s, a, chunk);                 \
   } while (0)
 #define OI_SCAN(MODE)                                 \
   do {                                                \

@@ -31,15 +31,17 @@ def runner_for(path, dtype, max_tokens=2048, max_requests=4, page_size=16, graph
     return r
 
 
-def compare(got, path, toks, dtype, what, rows=slice(None)):
-    assert_logits(got, oracle(path, toks)[rows], dtype, what, margin=router_margin(path, toks)[rows], noise=float32_noise(path, toks),
-                  noise16=bfloat16_noise(path, toks))
+def compare(got, path, toks, dtype, what, rows=slice(None), noise=None):
+    assert_logits(got, oracle(path, toks)[rows], dtype, what, margin=router_margin(path, toks)[rows],
+                  noise=float32_noise(path, toks) if noise is None else noise, noise16=bfloat16_noise(path, toks))
 
 
 def check_trace(runner, path, requests, steps, dtype, what):
     got = replay_in_process(runner, steps)
+    # what rounding alone does to this model: the largest of its sequences' samples (a short sequence is a poor sample)
+    noise = max(float32_noise(path, toks) for toks in requests.values())
     for rid, toks in requests.items():
-        compare(got[rid], path, toks, dtype, f"{what}/{rid}")
+        compare(got[rid], path, toks, dtype, f"{what}/{rid}", noise=noise)
     runner.cache.check()
     assert runner.cache.min_free_pages() == runner.cache.num_pages and runner.cache.slot_pool.used_count == 0
 
