@@ -577,20 +577,24 @@ def hyper_fanout(X: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
     return X
 
 
-def hyper_step(X: torch.Tensor, *, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+def hyper_step(X: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None, c1: float = 1.0,
+               c2: float = 0.0, mix: Optional[torch.Tensor] = None,
                b_out: Optional[torch.Tensor] = None, a_in: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
                eps: float = 0.0, weight_offset: float = 0.0, out: Optional[torch.Tensor] = None,
                row_idx: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """With ``y`` (float32 [tokens, width]): X[t, r] <- sum_s mix[s, r] X[t, s] + b_out[r] y[t] (in place; no coefficients:
-    X + y). With ``out``: out[t] = rms(sum_s a_in[s] X[t, s]) * (weight_offset + norm_w) from the new streams; ``row_idx``
+    X + y); with ``y2`` the result that comes back is c1 y + c2 y2 (two branches that were computed side by side). With ``out``: out[t] = rms(sum_s a_in[s] X[t, s]) * (weight_offset + norm_w) from the new streams; ``row_idx``
     gathers the rows that are read (then nothing is written to X)."""
     _cuda(X, y, mix, b_out, a_in, norm_w, out, row_idx)
     _i32(row_idx, "hyper_step row_idx")
     T, S, W = X.shape
     if X.dtype != torch.float32 or not X.is_contiguous():
         raise KernelError("hyper_step: the streams must be contiguous float32 [tokens, streams, width]")
-    if y is not None and (y.dtype != torch.float32 or y.shape != (T, W) or not y.is_contiguous()):
-        raise KernelError(f"hyper_step: y must be contiguous float32 [{T}, {W}], got {tuple(y.shape)} {y.dtype}")
+    for t in (y, y2):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (T, W) or not t.is_contiguous()):
+            raise KernelError(f"hyper_step: y must be contiguous float32 [{T}, {W}], got {tuple(t.shape)} {t.dtype}")
+    if y2 is not None and y is None:
+        raise KernelError("hyper_step: a second result needs a first")
     coefs = [t for t in (mix, b_out, a_in) if t is not None]
     for t, n in ((mix, S * S), (b_out, S), (a_in, S)):
         if t is not None and (t.numel() != n or not t.is_contiguous() or t.dtype != coefs[0].dtype):
@@ -599,7 +603,7 @@ def hyper_step(X: torch.Tensor, *, y: Optional[torch.Tensor] = None, mix: Option
     if out is not None and (out.shape != (rows, W) or not out.is_contiguous() or norm_w is None or norm_w.numel() != W):
         raise KernelError("hyper_step: out must be contiguous [rows, width] and the norm weight [width]")
     _lib.check(_lib.load().oi_hyper_step(
-        X.data_ptr(), rows, S, W, _ptr(y), 0, 1.0, 0.0, _ptr(mix), _ptr(b_out), _ptr(a_in), _code(coefs[0], "hyper_step") if coefs else 0,
+        X.data_ptr(), rows, S, W, _ptr(y), _ptr(y2), float(c1), float(c2), _ptr(mix), _ptr(b_out), _ptr(a_in), _code(coefs[0], "hyper_step") if coefs else 0,
         _ptr(norm_w), 0 if norm_w is None else _code(norm_w, "hyper_step norm"), float(eps), float(weight_offset), _ptr(out),
         0 if out is None else _code(out, "hyper_step out"), _ptr(row_idx), _stream()), "hyper_step")
     return out

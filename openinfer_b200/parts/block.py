@@ -141,6 +141,10 @@ class PendingBranch:
 
     y: torch.Tensor
     coefficients: Optional[Part] = None
+    # two results that were computed side by side and come back as c1 y + c2 y2 (formed by the kernel that carries them in)
+    y2: Optional[torch.Tensor] = None
+    c1: float = 1.0
+    c2: float = 0.0
 
 
 @register_block("hyper")
@@ -197,7 +201,9 @@ class HyperBlock(Block):
         """The pending result reaches the streams, and the next sublayer's input comes off them through its norm."""
         out = torch.empty((X.shape[0], X.shape[2]), dtype=dtype, device=X.device)
         c = pending.coefficients if pending is not None else None
-        ops.hyper_step(X, y=pending.y if pending is not None else None, mix=c.mix if c is not None else None,
+        ops.hyper_step(X, y=pending.y if pending is not None else None, y2=pending.y2 if pending is not None else None,
+                       c1=pending.c1 if pending is not None else 1.0, c2=pending.c2 if pending is not None else 0.0,
+                       mix=c.mix if c is not None else None,
                        b_out=c.b_out if c is not None else None, a_in=reader.a_in if reader is not None else None,
                        norm_w=norm.weight, eps=norm.spec.eps, weight_offset=norm.spec.weight_offset, out=out)
         return out
@@ -209,8 +215,11 @@ class HyperBlock(Block):
             raise RuntimeError("a hyper block follows hyper blocks only")
         dtype = ctx.scratch["model_dtype"]
         x = self.open_sublayer(h, pending, self.mixer_streams, self.input_norm, dtype)
-        a = self._mixer.forward(x, ctx, binding, out_dtype=torch.float32)
-        pending = PendingBranch(a, self.mixer_streams)
+        if getattr(self._mixer, "returns_pair", False):      # two sides whose weighted sum the next stream kernel forms
+            a, a2, c1, c2 = self._mixer.forward(x, ctx, binding, out_dtype=torch.float32, as_pair=True)
+            pending = PendingBranch(a, self.mixer_streams, y2=a2, c1=c1, c2=c2)
+        else:
+            pending = PendingBranch(self._mixer.forward(x, ctx, binding, out_dtype=torch.float32), self.mixer_streams)
         if self.feed_forward is not None:
             x = self.open_sublayer(h, pending, self.ff_streams, self.post_norm, dtype)
             m = self.feed_forward.forward(x, ctx, out_dtype=torch.float32)

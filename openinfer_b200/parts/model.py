@@ -434,7 +434,8 @@ class Model:
             # several streams: the last sublayer's result reaches them, then the wanted rows' streams are summed and normed
             if pending is not None:
                 c = pending.coefficients
-                ops.hyper_step(h, y=pending.y, mix=c.mix if c is not None else None, b_out=c.b_out if c is not None else None)
+                ops.hyper_step(h, y=pending.y, y2=pending.y2, c1=pending.c1, c2=pending.c2, mix=c.mix if c is not None else None,
+                               b_out=c.b_out if c is not None else None)
             n = self.final_norm
             x = torch.empty((row_idx.numel(), h.shape[2]), dtype=self.dtype, device=h.device)
             ops.hyper_step(h, norm_w=n.weight, eps=n.spec.eps, weight_offset=n.spec.weight_offset, out=x, row_idx=row_idx)

@@ -2,7 +2,8 @@
 
 The two are whatever mixers their specs name (an attention beside a recurrence, for instance); each keeps its own tensors
 under its own prefix, the cache entry is the one that asks for pages, and the state slots are the left's followed by the
-right's. Both hand their results back in float32, and one kernel forms the weighted sum.
+right's. Both hand their results back in float32; the weighted sum is formed by the kernel that carries a block's result into
+its streams when the block asks for the pair (``as_pair``), else by a kernel of its own.
 """
 from __future__ import annotations
 
@@ -21,6 +22,7 @@ from .spec import ParallelMixerSpec, ParamInfo
 @register_mixer("parallel")
 class ParallelMixer(Mixer):
     takes_out_dtype = True
+    returns_pair = True      # forward(as_pair=True) hands back both sides and their scales instead of the sum
 
     def __init__(self, spec: ParallelMixerSpec) -> None:
         super().__init__(spec)
@@ -56,12 +58,14 @@ class ParallelMixer(Mixer):
     def state_needs(self) -> List[StateNeed]:
         return self.left.state_needs() + self.right.state_needs()
 
-    def forward(self, x: torch.Tensor, ctx, binding: CacheBinding, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, binding: CacheBinding, out_dtype: Optional[torch.dtype] = None, as_pair: bool = False):
         n_left = len(self.left.state_needs())
         kv_left = self.left.kv_need() is not None
         lb = dataclasses.replace(binding, kv=binding.kv if kv_left else None, states=binding.states[:n_left])
         rb = dataclasses.replace(binding, kv=None if kv_left else binding.kv, states=binding.states[n_left:])
         a = self.left.forward(x, ctx, lb, out_dtype=torch.float32)
         b = self.right.forward(x, ctx, rb, out_dtype=torch.float32)
+        if as_pair:
+            return a, b, float(self.spec.left_scale), float(self.spec.right_scale)
         out = ops.scaled_sum(torch.empty_like(a), a, b, self.spec.left_scale, self.spec.right_scale)
         return out if out_dtype in (None, torch.float32) else out.to(out_dtype)

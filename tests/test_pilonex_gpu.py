@@ -83,6 +83,12 @@ def test_stream_kernels(S, W, out_dtype):
     ops.hyper_step(Xd, norm_w=_dev(w), eps=1e-5, weight_offset=1.0, out=out, row_idx=_dev(idx))
     ref = plain.rms_one_plus(Xn.sum(1), w.double(), 1e-5)[idx.long()]
     assert (out.double().cpu() - ref).abs().max().item() < tol * max(1.0, ref.abs().max().item()) and torch.equal(Xd, before)
+    # two results that come back as a weighted sum
+    y2 = torch.randn(T, W, generator=g)
+    Xd = _dev(X.clone())
+    ops.hyper_step(Xd, y=_dev(y), y2=_dev(y2), c1=1.3, c2=0.6, mix=_dev(M), b_out=_dev(b))
+    both = torch.einsum("tsw,sr->trw", X.double(), M.double()) + b.double()[None, :, None] * (1.3 * y.double() + 0.6 * y2.double())[:, None, :]
+    assert (Xd.double().cpu() - both).abs().max().item() < 1e-5 * max(1.0, both.abs().max().item())
     # without coefficients: x + y on every stream's own
     Xd = _dev(X.clone())
     ops.hyper_step(Xd, y=_dev(y))
