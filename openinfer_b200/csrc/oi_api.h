@@ -2,7 +2,8 @@
 //
 // All entry points return 0 on success or an error code (common.cuh); oi_last_error() gives the
 // message. Pointers are device pointers unless said otherwise; `stream` is a cudaStream_t. Element
-// type codes: OI_F32 = 0, OI_BF16 = 1. Activation codes: OI_ACT_NONE / OI_ACT_SILU / OI_ACT_GELU_TANH.
+// type codes: OI_F32 = 0, OI_BF16 = 1. Activation codes: OI_ACT_NONE / OI_ACT_SILU / OI_ACT_GELU_TANH / OI_ACT_XIELU /
+// OI_ACT_SWIGLU_CLAMP.
 #pragma once
 
 #include "common.cuh"
@@ -78,6 +79,48 @@ OI_API int oi_history_average(float* h, float* hist, long long hist_stride, int 
 OI_API int oi_short_conv(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, float*
        state, long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots, const int*
        state_phase, int tokens, int requests, int channels, int taps, int add_input, int update_state, void* stream);
+OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride, const void* x, int x_dtype, long long
+       x_stride, const void* w, int w_dtype, float* state, long long state_stride, const int* cu_seqlens, const int*
+       token_req, const int* state_slots, const int* state_phase, int tokens, int requests, int channels, int taps, int
+       add_input, int update_state, int act, void* stream);
+
+// elementwise.cu: every gated activation, the ones with a limit included (OI_ACT_SWIGLU_CLAMP)
+OI_API int oi_glu_act(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, float limit,
+       void* stream);
+
+// recurrent.cu: mixers with a matrix memory per head (mode 0: the mLSTM cell, 1: the gated delta rule)
+OI_API int oi_recurrent_record(int D);
+OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q_off, int k_off, int v_off, const float*
+       gates, long long ld_gates, int i_off, int f_off, const float* decay, long long ld_decay, const void* p0, const
+       void* p1, int p_dtype, float cap, float q_scale, float* prep, float* state, long long state_stride, const int*
+       cu_seqlens, const int* token_req, const int* state_slots, const int* state_phase, float* out, long long ld_out,
+       int tokens, int requests, int H, int G, int D, int V, void* stream);
+OI_API int oi_head_norm_gate(void* out, int out_dtype, long long ld_out, const float* o, long long ld_o, const float*
+       gate, long long ld_gate, const void* w, int w_dtype, int w_stride, int tokens, int H, int V, float eps, float
+       scale, void* stream);
+
+// hyper.cu: several residual streams
+OI_API int oi_hyper_step(float* X, int rows, int S, int W, const float* y, const float* y2, float c1, float c2, const
+       void* mix, const void* b_out, const void* a_in, int p_dtype, const void* norm_w, int nw_dtype, float eps, float
+       w_offset, void* out, int out_dtype, const int* row_idx, void* stream);
+OI_API int oi_hyper_fanout(float* X, const void* h, int h_dtype, int rows, int S, int W, void* stream);
+OI_API int oi_scaled_sum(float* out, const float* a, const float* b, float ca, float cb, long long n, void* stream);
+
+// moe.cu: routed experts
+OI_API int oi_moe_max_tiles(int pairs, int experts);
+OI_API int oi_moe_small(int pairs, int experts);
+OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int
+       E, int top, int* ids, float* wts, int* sorted, int* tile_info, void* stream);
+OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows,
+       int W, int F, int E, int top, float limit, const int* ids, const int* sorted, const int* tile_info, const float*
+       wts, void* act, float* y, float* out, void* stream);
+
+// gemm_stream.cu / gemm_tcgen05.cu: the gate/up product with a gated activation that takes a limit
+OI_API int oi_gemm_stream_glu(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W, long
+       long ldw, int M, int N, int K, int cluster_size, int act, float limit, void* stream);
+OI_API int oi_gemm_tcgen05_glu(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M,
+       int N, int K, int pair, int act, float limit, void* stream);
+
 OI_API int oi_latent_store(void* pages, long long page_stride, int page_size, int row_elems, const void* src, long
        long src_stride, int dtype, const void* w, int w_dtype, const int* slots, int tokens, int rank, float eps,
        float w_offset, void* stream);
