@@ -31,15 +31,35 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
   unsigned char* taken = reinterpret_cast<unsigned char*>(smem + E);
   const int row = blockIdx.x;
   const T* xr = x + (size_t)row * ldx;
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const bool vec = w_dtype == (sizeof(T) == 2 ? OI_BF16 : OI_F32) && K % kVec == 0 && ldx % kVec == 0 && (uintptr_t)x % 16 == 0 &&
+                   (uintptr_t)w % 16 == 0;
   // one block a row; a warp takes four experts at a time, so that their loads are in flight together
   for (int e0 = wi * 4; e0 < E; e0 += warps * 4) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int k = lane; k < K; k += 32) {
-      const float xv = to_f32(xr[k]);
+    if (vec) {       // a lane takes 16 bytes of the row and of each expert's weights at a time
+      const T* wt = reinterpret_cast<const T*>(w);
+#pragma unroll 2
+      for (int k = lane * kVec; k < K; k += 32 * kVec) {
+        T xv[kVec];
+        *reinterpret_cast<uint4*>(xv) = *reinterpret_cast<const uint4*>(xr + k);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (e0 + i < E) acc[i] += load_as_f32(w, w_dtype, (size_t)(e0 + i) * K + k) * xv;
+        for (int i = 0; i < 4; ++i)
+          if (e0 + i < E) {
+            T wv[kVec];
+            *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(wt + (size_t)(e0 + i) * K + k);
+#pragma unroll
+            for (int e = 0; e < kVec; ++e) acc[i] += to_f32(wv[e]) * to_f32(xv[e]);
+          }
+      }
+    } else {
+#pragma unroll 4
+      for (int k = lane; k < K; k += 32) {
+        const float xv = to_f32(xr[k]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (e0 + i < E) acc[i] += load_as_f32(w, w_dtype, (size_t)(e0 + i) * K + k) * xv;
+      }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

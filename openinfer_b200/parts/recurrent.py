@@ -148,7 +148,13 @@ class GatedDelta(Mixer):
         w[self.off_a: self.off_a + self.ra] = a1
         w[self.off_g: self.off_g + self.rg] = g1
         self.w_in = w.contiguous()
-        self.w_a2, self.w_g2 = a2.contiguous(), g2.contiguous()
+        # the second halves of the two low-rank products as ONE product over the neighbouring columns a1 | g1 of the fused
+        # sums: a block-diagonal matrix [H D + H V, pad8(ra) + pad8(rg)] (its zeros add exact zeros to the sums)
+        self.k_ag = _pad8(self.ra) + _pad8(self.rg)
+        w_ag = torch.zeros((a2.shape[0] + g2.shape[0], self.k_ag), dtype=a2.dtype, device=a2.device)
+        w_ag[: a2.shape[0], : self.ra] = a2
+        w_ag[a2.shape[0]:, _pad8(self.ra): _pad8(self.ra) + self.rg] = g2
+        self.w_ag = w_ag.contiguous()
         self.conv_w = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
         self.dt_bias = tensors["dt_bias"].contiguous()
         self.a_log = tensors["A_log"].to(self.dt_bias.dtype).contiguous()
@@ -172,8 +178,8 @@ class GatedDelta(Mixer):
         conv_state = ctx.cache.state_tensor(binding.states[1]) if s.conv_taps > 1 else None
         ops.short_conv_act(qkv, z[:, : self.filtered], self.conv_w, conv_state, ctx.cu_seqlens, ctx.token_req, ctx.state_slots,
                            ctx.state_phase, act="silu")
-        decay = linear(z[:, self.off_a: self.off_a + self.ra], self.w_a2, out_dtype=torch.float32)
-        gate = linear(z[:, self.off_g: self.off_g + self.rg], self.w_g2, out_dtype=torch.float32)
+        ag = linear(z[:, self.off_a: self.off_a + self.k_ag], self.w_ag, out_dtype=torch.float32)
+        decay, gate = ag[:, : H * D], ag[:, H * D:]
         o = torch.empty((T, H * V), dtype=torch.float32, device=x.device)
         ops.recurrent_scan(ops.SCAN_GATED_DELTA, o, qkv, (0, G * D, 2 * G * D), z, (self.off_b, 0),
                            ctx.cache.state_tensor(binding.states[0]), ctx, H, G, D, V, p0=self.dt_bias, p1=self.a_log, decay=decay,
