@@ -47,8 +47,8 @@ class PilonexConfig(ModelConfig):
             raise ConfigError(f"vocab and width must be positive, got {self.vocab} and {self.width}")
         if not isinstance(self.norm, dict) or not _number("norm", self.norm, "eps") > 0.0:
             raise ConfigError("norm.eps must be a number > 0")
-        if self.streams is not None and not 1 <= self.streams <= 8:
-            raise ConfigError(f"streams must be 1 to 8, got {self.streams}")
+        if self.streams is not None and not 1 <= self.streams <= 16:
+            raise ConfigError(f"streams must be 1 to 16, got {self.streams}")
         if not self.layers:
             raise ConfigError("'layers' must list at least one layer")
         if self.loop is not None:

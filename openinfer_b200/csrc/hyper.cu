@@ -8,13 +8,13 @@
 
 namespace {
 
-constexpr int kMaxStreams = 8;
+constexpr int kStreamLimit = 16;   // the kernels are built for up to 4, 8 and 16 streams
 
 // X [rows, S, W]. Part 1 (y != null): the streams of the row are mixed and y is added (y2 != null: y = c1 y + c2 y2).
 // Part 2 (out != null): out[row] = u * rsqrt(mean(u^2) + eps) * (w_offset + w), u = sum_s a[s] x_s (a null: the plain sum).
 // row_idx (part 2 alone): output row r reads the streams of row row_idx[r].
 // kVec: columns a thread handles side by side (4: 16-byte accesses, for widths that are a multiple of four).
-template <typename TO, int kVec>
+template <typename TO, int kVec, int kMaxStreams>
 __global__ void hyper_step_kernel(float* __restrict__ X, int S, int W, const float* __restrict__ y, const float* __restrict__ y2,
                                   float c1, float c2, const void* __restrict__ mix, const void* __restrict__ b_out,
                                   const void* __restrict__ a_in, int p_dtype, const void* __restrict__ norm_w, int nw_dtype,
@@ -138,19 +138,25 @@ int blocks_for(size_t n) { return (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : 
 OI_API int oi_hyper_step(float* X, int rows, int S, int W, const float* y, const float* y2, float c1, float c2, const void* mix,
                          const void* b_out, const void* a_in, int p_dtype, const void* norm_w, int nw_dtype, float eps,
                          float w_offset, void* out, int out_dtype, const int* row_idx, void* stream) {
-  OI_REQUIRE(rows >= 0 && S >= 1 && S <= kMaxStreams && W > 0, "hyper_step: bad sizes rows=%d streams=%d (at most %d) width=%d", rows,
-             S, kMaxStreams, W);
+  OI_REQUIRE(rows >= 0 && S >= 1 && S <= kStreamLimit && W > 0, "hyper_step: bad sizes rows=%d streams=%d (at most %d) width=%d", rows,
+             S, kStreamLimit, W);
   OI_REQUIRE(y != nullptr || out != nullptr, "hyper_step: nothing to do");
   OI_REQUIRE(row_idx == nullptr || y == nullptr, "hyper_step: rows are gathered for reading only");
   OI_REQUIRE(out == nullptr || norm_w != nullptr, "hyper_step: the norm needs its weight");
   if (rows == 0) return OI_OK;
   const bool vec = W % 4 == 0 && (uintptr_t)X % 16 == 0 && (y == nullptr || (uintptr_t)y % 16 == 0) && (y2 == nullptr || (uintptr_t)y2 % 16 == 0);
   const int cols = vec ? W / 4 : W;
-  const int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
+  const int threads = (cols >= 1024 || S > 8) ? 256 : (cols >= 256 ? 128 : 64);      // at least S * S threads
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_HYPER(TO, VEC)                                                                                                  \
-  oi_launch(hyper_step_kernel<TO, VEC>, rows, threads, 0, s, X, S, W, y, y2, c1, c2, mix, b_out, a_in, p_dtype, norm_w, nw_dtype, \
-            eps, w_offset, (TO*)out, row_idx)
+#define OI_HYPER_S(TO, VEC, MAXS)                                                                                          \
+  oi_launch(hyper_step_kernel<TO, VEC, MAXS>, rows, threads, 0, s, X, S, W, y, y2, c1, c2, mix, b_out, a_in, p_dtype, norm_w,     \
+            nw_dtype, eps, w_offset, (TO*)out, row_idx)
+#define OI_HYPER(TO, VEC)                    \
+  do {                                       \
+    if (S <= 4) OI_HYPER_S(TO, VEC, 4);      \
+    else if (S <= 8) OI_HYPER_S(TO, VEC, 8); \
+    else OI_HYPER_S(TO, VEC, 16);            \
+  } while (0)
   if (out_dtype == OI_BF16 && out != nullptr) {
     if (vec) OI_HYPER(bf16, 4);
     else OI_HYPER(bf16, 1);
@@ -159,6 +165,7 @@ OI_API int oi_hyper_step(float* X, int rows, int S, int W, const float* y, const
     else OI_HYPER(float, 1);
   }
 #undef OI_HYPER
+#undef OI_HYPER_S
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

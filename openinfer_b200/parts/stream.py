@@ -74,8 +74,8 @@ class StreamCoefficients(Part):
 
     def __init__(self, spec: StreamCoefficientsSpec) -> None:
         super().__init__(spec)
-        if not 1 <= spec.streams <= 8:
-            raise ValueError(f"stream_coefficients: {spec.streams} streams, 1 to 8 are supported")
+        if not 1 <= spec.streams <= 16:
+            raise ValueError(f"stream_coefficients: {spec.streams} streams, 1 to 16 are supported")
         self.a_in: Optional[torch.Tensor] = None
         self.mix: Optional[torch.Tensor] = None
         self.b_out: Optional[torch.Tensor] = None

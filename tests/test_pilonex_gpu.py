@@ -51,7 +51,7 @@ def _dev(t, dtype=None):
 
 
 # ---------------------------------------------------------------------------------------------- kernels alone
-@pytest.mark.parametrize("S,W", [(1, 40), (2, 64), (3, 100), (4, 1030), (8, 24)])
+@pytest.mark.parametrize("S,W", [(1, 40), (2, 64), (3, 100), (4, 1030), (5, 72), (8, 24), (11, 36), (16, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_stream_kernels(S, W, out_dtype):
     """The kernel that carries a sublayer's result into the streams and reads the next sublayer's normed input off the
@@ -295,6 +295,26 @@ def test_far_keys_and_old_state_reach_the_last_token(folders):
     compare(got, folders[name], toks, "float32", "far keys", rows=slice(200, None))
     other = plain.forward(cfg, tensors, [(toks[0] + 1) % cfg["vocab"]] + toks[1:])[200:]
     assert (ref - other).abs().max().item() > 100 * (got - ref).abs().max().item(), "the first token would not be missed"
+
+
+def test_a_far_key_among_hundreds_reaches_the_attention(tmp_path):
+    """Attention alone (the other side switched off), no window, a sharp softmax: a row's weight sits on the few keys
+    that match it best, wherever they are among 300. The engine follows the plain implementation while decoding, and a
+    plain implementation that sees only the last 200 keys does not."""
+    cfg = _one_layer(parallel(attn(4, 2, 16, 24, 1.2, rot={"dims": 8, "base": 10000.0}), delta(1, 1, 8, 8, 2), 1.0, 0.0, dense(64, 2.0)))
+    path = make_folder(str(tmp_path / "far"), cfg, 11)
+    raw, tensors = read_folder(path)
+    toks = tokens_for(cfg, 300, 5)
+    runner = runner_for(path, "float32", max_tokens=512)
+    got = replay_in_process(runner, trace_tail({"f": toks}, tail=60))["f"].double()
+    ref = oracle(path, toks)
+    compare(got, path, toks, "float32", "far key")
+    near = json.loads(json.dumps(raw))
+    near["layers"][0]["mixer"]["left"]["mask"] = {"size": 200}
+    wrong = plain.forward(near, tensors, toks)
+    scale = ref.pow(2).mean().sqrt().item()
+    assert (ref[240:] - wrong[240:]).abs().max().item() > 1e-2 * scale, "lost far keys would not be noticed"
+    assert (got[240:] - ref[240:]).abs().max().item() < 1e-4 * scale
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
