@@ -293,7 +293,7 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
   OI_REQUIRE(mode == kMatrixMemory || mode == kGatedDelta, "recurrent_scan: unknown mode %d", mode);
   OI_REQUIRE(requests >= 0 && tokens >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0,
              "recurrent_scan: bad sizes H=%d G=%d D=%d V=%d", H, G, D, V);
-  OI_REQUIRE(D <= 16 * kMaxRegs, "recurrent_scan: %d key channels per head, at most %d", D, 16 * kMaxRegs);
+  OI_REQUIRE(D <= 32 * kMaxRegs, "recurrent_scan: %d key channels per head, at most %d", D, 32 * kMaxRegs);
   OI_REQUIRE(mode != kGatedDelta || decay != nullptr, "recurrent_scan: the delta rule needs its decays");
   OI_REQUIRE(prep != nullptr, "recurrent_scan: the scratch for the rows' records is missing");
   const long long elems = (long long)D * V + (mode == kMatrixMemory ? D + 1 : 0);
@@ -312,7 +312,7 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
   if (mode == kMatrixMemory) oi_launch(recurrent_prepare_kernel<kMatrixMemory>, (warps + 3) / 4, 128, 0, s, a);
   else oi_launch(recurrent_prepare_kernel<kGatedDelta>, (warps + 3) / 4, 128, 0, s, a);
   OI_CHECK_LAUNCH();
-  const int chunk = D <= 64 ? 16 : (D <= 128 ? 8 : 4);   // rows per buffer: two buffers of at most 13 KB
+  const int chunk = D <= 64 ? 16 : (D <= 128 ? 8 : (D <= 256 ? 4 : 2));   // rows per buffer: two buffers of at most 13 KB
 #define OI_SCAN_AS(MODE, LANES, REGS)                                                                                   \
   do {                                                                                                                  \
     constexpr int cols = kThreads / LANES;                                                                              \
@@ -331,7 +331,8 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
     if (D <= 16) OI_SCAN_AS(MODE, 4, 4);              \
     else if (D <= 64) OI_SCAN_AS(MODE, 4, 16);        \
     else if (D <= 128) OI_SCAN_AS(MODE, 8, 16);       \
-    else OI_SCAN_AS(MODE, 16, 16);                    \
+    else if (D <= 256) OI_SCAN_AS(MODE, 16, 16);      \
+    else OI_SCAN_AS(MODE, 32, 16);                    \
   } while (0)
   if (mode == kMatrixMemory) OI_SCAN(kMatrixMemory);
   else OI_SCAN(kGatedDelta);

@@ -36,8 +36,8 @@ class Attention(Mixer):
         s = spec
         if s.num_heads % s.num_kv_heads:
             raise ValueError(f"num_heads ({s.num_heads}) must be a multiple of num_kv_heads ({s.num_kv_heads})")
-        if s.head_dim % 8 or s.head_dim > 256:
-            raise ValueError(f"head_dim {s.head_dim} unsupported: multiples of 8 up to 256")
+        if s.head_dim % 8 or s.head_dim > 512:
+            raise ValueError(f"head_dim {s.head_dim} unsupported: multiples of 8 up to 512")
         self.qk = s.qk_dim or s.head_dim
         self.vd = s.v_dim or s.head_dim
         if self.qk > s.head_dim or self.vd > s.head_dim:

@@ -43,8 +43,8 @@ class MatrixMemory(Mixer):
     def __init__(self, spec: MatrixMemorySpec) -> None:
         super().__init__(spec)
         s = spec
-        if min(s.num_heads, s.qk_dim, s.v_dim) <= 0 or s.qk_dim > 256 or not s.gate_cap > 0:
-            raise ValueError(f"matrix_memory: heads {s.num_heads}, dim {s.qk_dim} (at most 256), vdim {s.v_dim}, cap {s.gate_cap}")
+        if min(s.num_heads, s.qk_dim, s.v_dim) <= 0 or s.qk_dim > 512 or not s.gate_cap > 0:
+            raise ValueError(f"matrix_memory: heads {s.num_heads}, dim {s.qk_dim} (at most 512), vdim {s.v_dim}, cap {s.gate_cap}")
         H, D, V = s.num_heads, s.qk_dim, s.v_dim
         # columns of the fused product: q | k | v | output gate | zi | zf
         self.off = {"q": 0, "k": H * D, "v": 2 * H * D, "g": 2 * H * D + H * V, "i": 2 * H * D + 2 * H * V,
@@ -101,8 +101,8 @@ class GatedDelta(Mixer):
     def __init__(self, spec: GatedDeltaSpec) -> None:
         super().__init__(spec)
         s = spec
-        if min(s.num_heads, s.num_kv_heads, s.qk_dim, s.v_dim) <= 0 or s.num_heads % s.num_kv_heads or s.qk_dim > 256 or s.conv_taps < 1:
-            raise ValueError(f"gated_delta: heads {s.num_heads}, kv heads {s.num_kv_heads}, dim {s.qk_dim} (at most 256), "
+        if min(s.num_heads, s.num_kv_heads, s.qk_dim, s.v_dim) <= 0 or s.num_heads % s.num_kv_heads or s.qk_dim > 512 or s.conv_taps < 1:
+            raise ValueError(f"gated_delta: heads {s.num_heads}, kv heads {s.num_kv_heads}, dim {s.qk_dim} (at most 512), "
                              f"vdim {s.v_dim}, taps {s.conv_taps}")
         H, G, D, V = s.num_heads, s.num_kv_heads, s.qk_dim, s.v_dim
         self.filtered = 2 * G * D + H * V            # q | k | v: the columns that pass the filter

@@ -174,9 +174,12 @@ def _one_layer(layer, streams=None, width=48, vocab=83):
 MECHANISMS = {
     "matrix memory": _one_layer(mlstm(3, 16, 24, 5.0)),
     "matrix memory, one head, wide keys": _one_layer(mlstm(1, 100, 8, 15.0)),
+    "matrix memory with 300 key channels": _one_layer(mlstm(1, 300, 8, 10.0)),
     "window attention alone": _one_layer(parallel(attn(4, 2, 16, 8, 0.5, window=18, rot={"dims": 12, "base": 1000.0, "scaling": STRETCH}),
                                                   delta(2, 1, 8, 8, 2), 1.0, 0.0)),
     "attention with values wider than keys, no rotation, no window": _one_layer(parallel(attn(3, 3, 8, 20, 0.7), delta(1, 1, 8, 8, 1), 1.0, 0.0)),
+    "attention with heads wider than 256": _one_layer(parallel(attn(2, 1, 264, 40, 0.08, window=40, rot={"dims": 100, "base": 10000.0}),
+                                                               delta(1, 1, 8, 8, 2), 1.0, 0.0)),
     "delta rule alone": _one_layer(parallel(attn(1, 1, 8, 8, 1.0, window=4), delta(4, 2, 12, 20, 4), 0.0, 1.0)),
     "delta rule, one tap": _one_layer(parallel(attn(1, 1, 8, 8, 1.0, window=4), delta(3, 3, 16, 8, 1), 0.0, 1.0)),
     "routed experts": _one_layer(mlstm(1, 8, 8, 5.0, moe(32, 0.9, 7, 3))),
