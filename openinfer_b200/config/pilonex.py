@@ -96,8 +96,8 @@ class PilonexConfig(ModelConfig):
                         sc = _object(where + ".mixer.left.rot", rot, "scaling")
                         for key in ("factor", "low", "high", "original"):
                             _number(where + ".mixer.left.rot.scaling", sc, key)
-                        if sc["high"] == sc["low"] or sc["factor"] == 0:
-                            raise ConfigError(f"{where}.mixer.left.rot.scaling: high must differ from low and factor from 0")
+                        if sc["factor"] == 0:
+                            raise ConfigError(f"{where}.mixer.left.rot.scaling: factor must differ from 0")
             mlp = layer.get("mlp")
             if mlp is not None:
                 if not isinstance(mlp, dict) or mlp.get("kind") not in MLP_KINDS:

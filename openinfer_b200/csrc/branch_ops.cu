@@ -97,11 +97,27 @@ __global__ void history_average_kernel(float* __restrict__ h, float* __restrict_
 // ---------------------------------------------------------------------------------------------
 template <typename TX, typename TO>
 __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype,
-                                  const float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
+                                  float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ token_req, const int* __restrict__ state_slots,
                                   const int* __restrict__ state_phase, int channels, int taps, int add_input,
-                                  long long x_stride, long long out_stride, int act) {
+                                  long long x_stride, long long out_stride, int act, int tokens) {
   pdl_start();
+  if ((int)blockIdx.x >= tokens) {
+    // behind the filter's blocks, one block per request (and chunk of channels) leaves the new state in the other copy:
+    // the last taps - 1 inputs of (current copy, this step's rows)
+    const int b = blockIdx.x - tokens, keep = taps - 1;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    if (n <= 0 || token_req[start] < 0) return;   // a padding request of a recorded step owns no state
+    const int phase = state_phase[b];
+    const float* old = state + (size_t)state_slots[b] * state_stride + (size_t)phase * keep * channels;
+    float* st = state + (size_t)state_slots[b] * state_stride + (size_t)(1 - phase) * keep * channels;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x)
+      for (int k = 0; k < keep; ++k) {
+        const int s = n + k - keep;
+        st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * x_stride + c]) : old[(size_t)(k + n) * channels + c];
+      }
+    return;
+  }
   const int t = blockIdx.x;
   const int req = token_req[t];
   const int start = req >= 0 ? cu_seqlens[req] : t;
@@ -123,27 +139,6 @@ __global__ void short_conv_kernel(TO* __restrict__ out, const TX* __restrict__ x
     }
     if (act == OI_ACT_SILU) acc = acc / (1.f + expf(-acc));
     out[(size_t)t * out_stride + c] = from_f32<TO>(acc);
-  }
-}
-
-// the other copy of the state <- the last taps - 1 inputs of (current copy, this step's rows), per request and channel
-template <typename TX>
-__global__ void short_conv_state_kernel(float* __restrict__ state, long long state_stride, const TX* __restrict__ x,
-                                        const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
-                                        const int* __restrict__ state_slots, const int* __restrict__ state_phase, int channels,
-                                        int keep, long long x_stride) {
-  pdl_start();
-  const int b = blockIdx.x;
-  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
-  if (n <= 0 || token_req[start] < 0) return;   // a padding request of a recorded step owns no state
-  const int phase = state_phase[b];
-  const float* old = state + (size_t)state_slots[b] * state_stride + (size_t)phase * keep * channels;
-  float* st = state + (size_t)state_slots[b] * state_stride + (size_t)(1 - phase) * keep * channels;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-    for (int k = 0; k < keep; ++k) {
-      const int s = n + k - keep;
-      st[(size_t)k * channels + c] = s >= 0 ? to_f32(x[(size_t)(start + s) * x_stride + c]) : old[(size_t)(k + n) * channels + c];
-    }
   }
 }
 
@@ -553,15 +548,11 @@ OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride,
       OI_CHECK_LAUNCH();                                                                                                 \
       return OI_OK;                                                                                                      \
     }                                                                                                                    \
-    oi_launch(short_conv_kernel<TX, TO>, grid, kRowThreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, (const float*)state, \
-              state_stride, cu_seqlens, token_req, state_slots, state_phase, channels, taps, add_input, x_stride,        \
-              out_stride, act);                                                                                          \
+    /* the filter's blocks, and behind them one block per request (and chunk of channels) that leaves the new state */    \
+    oi_launch(short_conv_kernel<TX, TO>, dim3(tokens + ((update_state && taps > 1) ? requests : 0), cy), kRowThreads, 0, s, \
+              (TO*)out, (const TX*)x, w, w_dtype, state, state_stride, cu_seqlens, token_req, state_slots, state_phase,  \
+              channels, taps, add_input, x_stride, out_stride, act, tokens);                                             \
     OI_CHECK_LAUNCH();                                                                                                   \
-    if (update_state && taps > 1) {                                                                                      \
-      oi_launch(short_conv_state_kernel<TX>, dim3(requests, cy), kRowThreads, 0, s, state, state_stride, (const TX*)x,    \
-                cu_seqlens, token_req, state_slots, state_phase, channels, taps - 1, x_stride);                          \
-      OI_CHECK_LAUNCH();                                                                                                 \
-    }                                                                                                                    \
     return OI_OK;                                                                                                        \
   }
   OI_CONV_CASE(OI_F32, OI_F32, float, float)

@@ -52,7 +52,8 @@ class RotaryEncoding(PositionEncoding):
                 idx = torch.arange(half, dtype=torch.float64)
                 f = float(s.theta) ** (-2.0 * idx / s.rotary_dim)
                 wave = 2.0 * math.pi / f
-                t = (original / wave - low) / (high - low)
+                # (high == low leaves no band between the two regimes: nothing is mixed)
+                t = (original / wave - low) / (high - low) if high != low else torch.zeros_like(wave)
                 f = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, (1.0 - t) * f / factor + t * f))
                 f = f.to(torch.float32).to(torch.float64)
                 ang = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * f[None, :]
