@@ -148,7 +148,7 @@ def test_routed_experts_kernels(dtype, rows, W, F, E, top):
 def test_stretched_rotation_tables():
     from openinfer_b200.parts.position import RotaryEncoding
     from openinfer_b200.parts.spec import PositionSpec
-    for dims, base, sc in ((8, 10000.0, STRETCH), (64, 500000.0, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}), (6, 100.0, None)):
+    for dims, base, sc in ((8, 10000.0, STRETCH), (64, 200000.0, {"factor": 3.0, "low": 1.0, "high": 5.0, "original": 256}), (6, 100.0, None)):
         spec = PositionSpec(kind="rope", rotary_dim=dims, theta=base, max_positions=700,
                             scaling=(sc["factor"], sc["low"], sc["high"], sc["original"]) if sc else None)
         cos, sin = RotaryEncoding(spec).rotation_tables(torch.device("cuda"))
