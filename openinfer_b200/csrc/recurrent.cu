@@ -196,8 +196,63 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
     __syncthreads();
     const float* stage_now = stage + (size_t)turn * buf_floats;
     const float* vals = stage_now + (size_t)chunk * rec;
+    int tt = 0;
+    if (kMode == kGatedDelta) {
+      // Two rows at a time. With A = g1 C (the state behind the first row's decay) everything the two rows need of the
+      // state is four dot products with A that do not wait for one another:
+      //   d1 = b1 (v1 - A^T k1),  o1 = A^T q1 + (k1 . q1) d1,
+      //   d2 = b2 (v2 - (g2 A)^T k2 - ((g2 k1) . k2) d1),  o2 = (g2 A)^T q2 + ((g2 k1) . q2) d1 + (k2 . q2) d2,
+      //   C <- g2 A + (g2 k1) d1 + k2 d2,
+      // so the chain from state to state holds one tree of shuffles a pair instead of two a row.
+      for (; tt + 1 < n; tt += 2) {
+        const float* r1 = stage_now + (size_t)tt * rec;
+        const float* r2 = r1 + rec;
+        const float v1 = vals[tt * kCols + cl], v2 = vals[(tt + 1) * kCols + cl];
+        const float b1 = r1[3 * D], b2 = r2[3 * D];
+        float k1[R], q1[R], k2[R], q2[R], g[R];
+        load_channels<kLanes, R, kVec4>(g, r1 + 2 * D, D, j);
+        load_channels<kLanes, R, kVec4>(k1, r1, D, j);
+        load_channels<kLanes, R, kVec4>(q1, r1 + D, D, j);
+        float ak1[4] = {0.f, 0.f, 0.f, 0.f}, aq1[4] = {0.f, 0.f, 0.f, 0.f}, s1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          C[i] *= g[i];
+          ak1[i & 3] += C[i] * k1[i];
+          aq1[i & 3] += C[i] * q1[i];
+          s1 += k1[i] * q1[i];
+        }
+        load_channels<kLanes, R, kVec4>(g, r2 + 2 * D, D, j);
+        load_channels<kLanes, R, kVec4>(k2, r2, D, j);
+        load_channels<kLanes, R, kVec4>(q2, r2 + D, D, j);
+        float ak2[4] = {0.f, 0.f, 0.f, 0.f}, aq2[4] = {0.f, 0.f, 0.f, 0.f}, s2 = 0.f, s3 = 0.f, s4 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          C[i] *= g[i];                 // g2 A
+          k1[i] *= g[i];                // g2 k1
+          ak2[i & 3] += C[i] * k2[i];
+          aq2[i & 3] += C[i] * q2[i];
+          s2 += k1[i] * k2[i];
+          s3 += k1[i] * q2[i];
+          s4 += k2[i] * q2[i];
+        }
+        const float A_k1 = lanes_sum<kLanes>((ak1[0] + ak1[1]) + (ak1[2] + ak1[3]));
+        const float A_q1 = lanes_sum<kLanes>((aq1[0] + aq1[1]) + (aq1[2] + aq1[3]));
+        const float A_k2 = lanes_sum<kLanes>((ak2[0] + ak2[1]) + (ak2[2] + ak2[3]));
+        const float A_q2 = lanes_sum<kLanes>((aq2[0] + aq2[1]) + (aq2[2] + aq2[3]));
+        s1 = lanes_sum<kLanes>(s1), s2 = lanes_sum<kLanes>(s2), s3 = lanes_sum<kLanes>(s3), s4 = lanes_sum<kLanes>(s4);
+        const float d1 = b1 * (v1 - A_k1);
+        const float d2 = b2 * (v2 - (A_k2 + s2 * d1));
+#pragma unroll
+        for (int i = 0; i < R; ++i) C[i] += k1[i] * d1 + k2[i] * d2;
+        if (j == 0 && col) {
+          float* o_row = a.out + (size_t)(start + t0 + tt) * a.ld_out + (size_t)h * V + c;
+          o_row[0] = A_q1 + s1 * d1;
+          o_row[a.ld_out] = A_q2 + s3 * d1 + s4 * d2;
+        }
+      }
+    }
 #pragma unroll 2
-    for (int tt = 0; tt < n; ++tt) {
+    for (; tt < n; ++tt) {
       const float* r = stage_now + (size_t)tt * rec;
       const float v = vals[tt * kCols + cl];
       float o;
