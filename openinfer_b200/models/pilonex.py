@@ -33,7 +33,7 @@ def _mixer(cfg: PilonexConfig, layer: dict, eps: float):
     if rot:
         sc = rot.get("scaling")
         position = PositionSpec(kind="rope", rotary_dim=int(rot["dims"]), theta=float(rot["base"]),
-                                max_positions=cfg.max_position_embeddings,
+                                max_positions=cfg.max_position_embeddings, precise=True,
                                 scaling=(float(sc["factor"]), float(sc["low"]), float(sc["high"]), float(sc["original"])) if sc else None)
     attention = AttentionSpec(
         hidden_size=W, num_heads=int(left["heads"]), num_kv_heads=int(left["kv_heads"]), head_dim=_pad8(max(dim, vdim)),

@@ -37,25 +37,23 @@ class RotaryEncoding(PositionEncoding):
 
     def rotation_tables(self, device: torch.device):
         s = self.spec
-        key = (s.rotary_dim, float(s.theta), s.max_positions, s.scaling, str(device))
+        key = (s.rotary_dim, float(s.theta), s.max_positions, s.scaling, s.precise, str(device))
         if key not in _TABLES:
             half = s.rotary_dim // 2
-            if s.scaling is None:
+            if s.scaling is None and not s.precise:
                 idx = torch.arange(half, dtype=torch.float32)
                 inv_freq = 1.0 / torch.pow(torch.tensor(float(s.theta), dtype=torch.float32),
                                            idx * 2.0 / s.rotary_dim)
                 ang = torch.arange(s.max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
             else:
-                # stretched long waves: the frequencies are formed in float64 and rounded once to float32; the angle is
-                # the exact product of the position and that float32 frequency
-                factor, low, high, original = (float(v) for v in s.scaling)
+                # stretched long waves: frequencies and angles are formed in float64; cos and sin are rounded once to float32
                 idx = torch.arange(half, dtype=torch.float64)
                 f = float(s.theta) ** (-2.0 * idx / s.rotary_dim)
+                factor, low, high, original = (float(v) for v in s.scaling) if s.scaling is not None else (1.0, 1.0, 2.0, 1.0)
                 wave = 2.0 * math.pi / f
                 # (high == low leaves no band between the two regimes: nothing is mixed)
                 t = (original / wave - low) / (high - low) if high != low else torch.zeros_like(wave)
                 f = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, (1.0 - t) * f / factor + t * f))
-                f = f.to(torch.float32).to(torch.float64)
                 ang = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * f[None, :]
             _TABLES[key] = (torch.cos(ang).to(torch.float32).contiguous().to(device),
                             torch.sin(ang).to(torch.float32).contiguous().to(device))

@@ -49,6 +49,7 @@ class PositionSpec:
     # l < original / high, becomes f / factor for l > original / low, and in between (1 - s) f / factor + s f with
     # s = (original / l - low) / (high - low)
     scaling: Optional[Tuple[float, float, float, float]] = None
+    precise: bool = False       # frequencies and angles in float64 (cos and sin rounded once); False: float32 throughout
 
 
 @dataclasses.dataclass(frozen=True)
